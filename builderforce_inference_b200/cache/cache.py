@@ -41,6 +41,7 @@ class KVView:
     page_tokens: int = PAGE_TOKENS
     v_dim: Optional[int] = None        # None: as head_dim
     chunk: Optional[int] = None        # a token reads only its own block of `chunk` positions
+    values_in_keys: bool = False       # a value is the first v_dim values of its key; `v` is `k`
 
     @property
     def value_dim(self) -> int:
@@ -49,7 +50,7 @@ class KVView:
     @property
     def plain(self) -> bool:
         """Keys and values of one size and no chunked mask: what every attention kernel takes."""
-        return self.value_dim == self.head_dim and self.chunk is None
+        return self.value_dim == self.head_dim and self.chunk is None and not self.values_in_keys
 
 
 @dataclass
@@ -85,7 +86,10 @@ class _KVGroup:
         self.n_blocks = n_blocks
         self.device = device
         self.storage = self.v_storage = None
-        if need.value_dim == need.head_dim:
+        if need.values_in_keys:     # keys only: the values are read out of them
+            self.storage = torch.empty((len(keys), 1, n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim),
+                                       dtype=dtype, device=device)
+        elif need.value_dim == need.head_dim:
             self.storage = torch.empty(
                 (len(keys), 2, n_pages, need.n_kv_heads, PAGE_TOKENS, need.head_dim),
                 dtype=dtype, device=device)
@@ -120,13 +124,17 @@ class _KVGroup:
 
     def view(self, key) -> KVView:
         i = self.keys.index(key)
-        v = self.storage[i, 1] if self.v_storage is None else self.v_storage[i]
+        if self.need.values_in_keys:
+            v = self.storage[i, 0]
+        else:
+            v = self.storage[i, 1] if self.v_storage is None else self.v_storage[i]
         return KVView(k=self.storage[i, 0], v=v, block_table=self.block_dev,
                       n_kv_heads=self.need.n_kv_heads, head_dim=self.need.head_dim,
-                      window=self.need.window, v_dim=self.need.v_dim, chunk=self.need.chunk)
+                      window=self.need.window, v_dim=self.need.v_dim, chunk=self.need.chunk,
+                      values_in_keys=self.need.values_in_keys)
 
     def bytes_per_token(self) -> int:
-        return len(self.runs) * self.need.n_kv_heads * (self.need.head_dim + self.need.value_dim) * self.storage.element_size()
+        return len(self.runs) * self.need.n_kv_heads * self.need.stored_per_head * self.storage.element_size()
 
     def fill(self, value: float) -> None:
         self.storage.fill_(value)
@@ -165,14 +173,16 @@ class SequenceCache:
     """Slots, pages and fixed-size state for the live sequences of one model.
 
     ``needs[i]`` is what run ``i`` of the schedule keeps (None for nothing); ``cache_of[i]``
-    names the run whose cache run ``i`` reads instead of keeping its own.
+    names the run whose cache run ``i`` reads instead of keeping its own.  ``model_needs[j]`` is
+    what part ``j`` outside the layers keeps (an input part's state); ``model_cache(j)`` hands it out.
     ``max_tokens`` is the most tokens all live sequences hold together, each sequence's count
     rounded up to a whole page; ``max_seq_len`` the most one sequence may hold.
     """
 
     def __init__(self, needs: Sequence[Union[KVNeed, StateNeed, None]],
                  cache_of: Sequence[Optional[int]], max_tokens: int, max_seq_len: int,
-                 dtype: torch.dtype, device: torch.device, initial_slots: int = 64):
+                 dtype: torch.dtype, device: torch.device, initial_slots: int = 64,
+                 model_needs: Sequence[Any] = ()):
         if max_tokens < 1 or max_seq_len < 1:
             raise CacheError("max_tokens and max_seq_len must be positive")
         self.device = torch.device(device)
@@ -200,6 +210,14 @@ class SequenceCache:
             for j, one in enumerate(needs_of(need)):
                 # a run that names the same need twice gets two places in that need's group
                 by_need.setdefault(one, []).append((run, j))
+        # parts outside the layers keep theirs under keys of their own, past the runs
+        self._model_keys = []
+        for j, need in enumerate(model_needs):
+            key_run = ("model", j)
+            self._model_keys.append(key_run)
+            self._owner[key_run] = []
+            for k, one in enumerate(needs_of(need)):
+                by_need.setdefault(one, []).append((key_run, k))
         for need, keys in by_need.items():
             if isinstance(need, KVNeed):
                 g = _KVGroup(need, keys, self.n_pages, n_slots, self.n_blocks, dtype, self.device)
@@ -223,6 +241,14 @@ class SequenceCache:
         kv = next((e for e in entries if isinstance(e, KVView)), None)
         state = next((e for e in entries if not isinstance(e, KVView)), None)
         return RunCache(kv=kv, state=state, writes_cache=src is None, entries=entries)
+
+    def model_cache(self, j: int) -> RunCache:
+        """What part ``j`` of ``model_needs`` keeps, in the form a run's cache has."""
+        entries = tuple(g.view(key) if isinstance(g, _KVGroup) else g.storage[key]
+                        for _, g, key in self._owner.get(self._model_keys[j], ()))
+        kv = next((e for e in entries if isinstance(e, KVView)), None)
+        state = next((e for e in entries if not isinstance(e, KVView)), None)
+        return RunCache(kv=kv, state=state, writes_cache=True, entries=entries)
 
     # ---- slots -----------------------------------------------------------------------
     def acquire(self) -> int:

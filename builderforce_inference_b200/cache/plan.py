@@ -55,7 +55,7 @@ def _own_needs(needs, cache_of):
 def kv_bytes_per_token(needs: Sequence, cache_of: Sequence[Optional[int]], elem_bytes: int) -> int:
     """Bytes of keys and values one token of cache capacity costs, over all runs that keep a
     cache of their own."""
-    return sum(n.n_kv_heads * (n.head_dim + n.value_dim) * elem_bytes for n in _own_needs(needs, cache_of)
+    return sum(n.n_kv_heads * n.stored_per_head * elem_bytes for n in _own_needs(needs, cache_of)
                if isinstance(n, KVNeed))
 
 

@@ -12,6 +12,8 @@
 // query sees and that has no value: p_j = exp(s_j) / (exp(sink) + sum_i exp(s_i)); the sink is one
 // number (`has_sink` 1) or one float32 per query head (`has_sink` 2, `sinks`).
 // Keys have `d` values per head, values `dv` (the cache's value pages are laid out by `dv`).
+// Without value pages (`v_pages` null) a key's first `dv` values are its value: the cache of a
+// latent attention holds one row per token that serves as both.
 //
 // Work split: one block per (sequence, kv head, chunk of heads of its group, chunk of tokens);
 // 16 query rows per block (GH heads x 16/GH consecutive tokens) share each tile of 32 keys that
@@ -109,12 +111,14 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
             if (page >= 0 && key >= lo && key <= hi) kv = to_f32(k_pages[base + (size_t)j * d + e]);
             ks[j * (d + 1) + e] = kv;
         }
-        for (int i = threadIdx.x; i < ATT_KEYS * dv; i += blockDim.x) {
-            const int j = i / dv, e = i - j * dv;
-            const int key = kb + j;
-            float vv = 0.0f;
-            if (page >= 0 && key >= lo && key <= hi) vv = to_f32(v_pages[base_v + (size_t)j * dv + e]);
-            vs[j * dv + e] = vv;
+        if (v_pages != nullptr) {
+            for (int i = threadIdx.x; i < ATT_KEYS * dv; i += blockDim.x) {
+                const int j = i / dv, e = i - j * dv;
+                const int key = kb + j;
+                float vv = 0.0f;
+                if (page >= 0 && key >= lo && key <= hi) vv = to_f32(v_pages[base_v + (size_t)j * dv + e]);
+                vs[j * dv + e] = vv;
+            }
         }
         __syncthreads();
 
@@ -144,7 +148,7 @@ attention_paged_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ o
             for (int jj = 0; jj < ATT_KEYS; ++jj) {
                 const float pj = __shfl_sync(0xffffffffu, p, jj);
                 if (pj == 0.0f) continue;
-                const float* vr = vs + jj * dv;
+                const float* vr = v_pages != nullptr ? vs + jj * dv : ks + jj * (d + 1);
 #pragma unroll
                 for (int c = 0; c < NC; ++c) {
                     const int e = lane + 32 * c;
@@ -187,7 +191,7 @@ static int launch_attention(const void* q, long q_stride, void* out, long out_st
     dim3 grid((max_tokens + qt - 1) / qt, n_kv * head_chunks, n_seqs);
     BFI_REQUIRE(grid.y <= 65535 && grid.z <= 65535, "attention_paged: too many heads (%d) or sequences (%d) for one launch",
                 (int)grid.y, n_seqs);
-    const size_t smem = (size_t)(ATT_ROWS * d + ATT_KEYS * (d + 1) + ATT_KEYS * dv) * sizeof(float);
+    const size_t smem = (size_t)(ATT_ROWS * d + ATT_KEYS * (d + 1) + (v_pages ? ATT_KEYS * dv : 0)) * sizeof(float);
     auto kernel = attention_paged_kernel<T, NC>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -237,6 +241,7 @@ extern "C" int bfi_attention_paged(const void* q, int dtype, long q_stride, void
     BFI_REQUIRE(d > 0 && d % 2 == 0 && d <= ATT_MAX_D, "attention_paged: head_dim %d must be even, at most %d",
                 d, ATT_MAX_D);
     BFI_REQUIRE(dv > 0 && dv <= ATT_MAX_D, "attention_paged: value size %d must be positive, at most %d", dv, ATT_MAX_D);
+    BFI_REQUIRE(v_pages != nullptr || dv <= d, "attention_paged: values that are the keys' first %d values need keys that long", dv);
     BFI_REQUIRE(window >= 0 && chunk >= 0, "attention_paged: negative window or chunk");
     BFI_REQUIRE(has_sink != 2 || sinks != nullptr, "attention_paged: a sink per head needs its array");
     BFI_REQUIRE(q_stride >= (long)n_q * d && out_stride >= (long)n_q * dv, "attention_paged: token stride shorter than the heads");

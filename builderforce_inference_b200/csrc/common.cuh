@@ -175,17 +175,36 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 // The gated activation of a feed-forward, as the matrix products' gated epilogue applies it to a
-// (gate, up) pair: with g' = min(g, limit) and u' = clamp(u, -limit, limit) (limit <= 0: no clamping)
+// (gate, up) pair.  Kind 0, the sigmoid family: with g' = min(g, limit) and u' = clamp(u, -limit, limit)
+// (limit <= 0: no clamping)
 //     g' * sigmoid(alpha * g') * (u' + shift)
 // alpha 1, no limit and shift 0 is SiLU(gate) * up, and evaluates to the same bits as that formula.
+// Kind 1, the tanh form of GELU:  0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u.
 // A library holds ONE set of constants per host thread (bfi_set_gate), which every product launched
 // from that thread with the gated epilogue takes along as a kernel argument.
+#define BFI_GATE_SIGMOID 0
+#define BFI_GATE_GELU_TANH 1
 struct GateAct {
     float alpha, limit, shift;
+    int kind;
 };
 extern thread_local GateAct g_bfi_gate;
 
+// 0.5 g (1 + tanh(y)) = g * sigmoid(2 y): one exponential, no cancellation for large |y|
+__device__ __forceinline__ float gelu_tanh_exact(float g) {
+    const float y = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    float s;
+    if (y >= 0.0f) {
+        s = 1.0f / (1.0f + expf(-2.0f * y));
+    } else {
+        const float e = expf(2.0f * y);
+        s = e / (1.0f + e);
+    }
+    return g * s;
+}
+
 __device__ __forceinline__ float gate_mul_exact(float g, float u, const GateAct a) {
+    if (a.kind == BFI_GATE_GELU_TANH) return gelu_tanh_exact(g) * u;
     if (a.limit > 0.0f) {
         g = fminf(g, a.limit);
         u = fminf(fmaxf(u, -a.limit), a.limit);
@@ -201,6 +220,10 @@ __device__ __forceinline__ float gate_mul_exact(float g, float u, const GateAct 
     return g * s * (u + a.shift);
 }
 __device__ __forceinline__ float gate_mul_fast(float g, float u, const GateAct a) {
+    if (a.kind == BFI_GATE_GELU_TANH) {
+        const float y = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        return __fdividef(g, 1.0f + __expf(-2.0f * y)) * u;
+    }
     if (a.limit > 0.0f) {
         g = fminf(g, a.limit);
         u = fminf(fmaxf(u, -a.limit), a.limit);

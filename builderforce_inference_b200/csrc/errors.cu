@@ -32,10 +32,19 @@ extern "C" int bfi_set_pdl(int on) {
 }
 
 // The constants of the gated epilogue for the products this host thread launches from now on.
-thread_local GateAct g_bfi_gate = {1.0f, 0.0f, 0.0f};
+thread_local GateAct g_bfi_gate = {1.0f, 0.0f, 0.0f, BFI_GATE_SIGMOID};
 
 extern "C" int bfi_set_gate(float alpha, float limit, float shift) {
     g_bfi_gate.alpha = alpha, g_bfi_gate.limit = limit, g_bfi_gate.shift = shift;
+    g_bfi_gate.kind = BFI_GATE_SIGMOID;
+    return 0;
+}
+
+// The same, naming the activation's kind (BFI_GATE_*) as well.
+extern "C" int bfi_set_gate_kind(int kind, float alpha, float limit, float shift) {
+    if (kind != BFI_GATE_SIGMOID && kind != BFI_GATE_GELU_TANH) return bfi_fail("set_gate_kind: unknown activation kind %d", kind);
+    g_bfi_gate.alpha = alpha, g_bfi_gate.limit = limit, g_bfi_gate.shift = shift;
+    g_bfi_gate.kind = kind;
     return 0;
 }
 

@@ -10,6 +10,11 @@
 //     a tie; the weights are the chosen experts' s (not renormalised) times `weight_scale`.
 //     With `extra` (a logit beside the experts', column E of z) gate[t] = sigmoid(z_E): the factor
 //     of an expert that every token uses.
+//     `score_mode` 1: s = sigmoid(z), every expert by itself, instead of the softmax.
+//     `group_top` g > 1: a group's score is the sum of its g largest choice scores (of all of them,
+//     if it has fewer) instead of the largest.
+// `act_kind` of the experts: 0 = silu(gate) * up over interleaved gate and up rows (W_gu as below);
+//     1 = relu(up)^2, no gate: W_gu is then [E * ff, width], expert e's up row j at row e ff + j.
 // bfi_moe_router: the same decision with the logits made here, z = W_router h (float32 rows of W).
 // bfi_moe_gate_up:  act[t, k, :] = silu(W_gate[e] h_t) * (W_up[e] h_t),  e = idx[t, k]
 // bfi_moe_down:     out[t, :] (= | +=) sum_k weight[t, k] * W_down[idx[t, k]] act[t, k, :]
@@ -35,28 +40,55 @@ __device__ __forceinline__ float moe_sigmoid(float x) {
 __device__ __forceinline__ void moe_route_token(const float* zr, const float* __restrict__ correction, int* __restrict__ idx,
                                                 float* __restrict__ weight, float* __restrict__ gate, float* s, float* choice,
                                                 float* gs, int t, int E, int top, int n_groups, int keep, float weight_scale,
-                                                int extra, int lane) {
-    float m = -INFINITY;
-    for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
-    m = warp_max(m);
-    float sum = 0.0f;
-    for (int e = lane; e < E; e += 32) {
-        const float p = expf(zr[e] - m);
-        s[e] = p;
-        sum += p;
-    }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int e = lane; e < E; e += 32) {
-        s[e] *= inv;
-        choice[e] = s[e] + (correction ? correction[e] : 0.0f);
+                                                int extra, int lane, int score_mode, int group_top) {
+    if (score_mode == 1) {
+        for (int e = lane; e < E; e += 32) {
+            s[e] = moe_sigmoid(zr[e]);
+            choice[e] = s[e] + (correction ? correction[e] : 0.0f);
+        }
+    } else {
+        float m = -INFINITY;
+        for (int e = lane; e < E; e += 32) m = fmaxf(m, zr[e]);
+        m = warp_max(m);
+        float sum = 0.0f;
+        for (int e = lane; e < E; e += 32) {
+            const float p = expf(zr[e] - m);
+            s[e] = p;
+            sum += p;
+        }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < E; e += 32) {
+            s[e] *= inv;
+            choice[e] = s[e] + (correction ? correction[e] : 0.0f);
+        }
     }
     __syncwarp();
     const int per = E / n_groups;
     if (n_groups > 1 && keep < n_groups) {
         for (int g = lane; g < n_groups; g += 32) {
             float best = -INFINITY;
-            for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, choice[e]);
+            if (group_top <= 1) {
+                for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, choice[e]);
+            } else {
+                // the sum of the group's `group_top` largest, picked one after the other; what an
+                // earlier round picked is known by (value, position), so equal values count each
+                best = 0.0f;
+                int last_at = -1;
+                float last_v = INFINITY;
+                for (int r = 0; r < group_top && r < per; ++r) {
+                    float bv = -INFINITY;
+                    int ba = -1;
+                    for (int e = g * per; e < (g + 1) * per; ++e) {
+                        const float v = choice[e];
+                        const bool open = v < last_v || (v == last_v && e > last_at);   // not picked in an earlier round
+                        if (open && (v > bv || ba < 0)) bv = v, ba = e;
+                    }
+                    if (ba < 0) break;
+                    best += bv;
+                    last_v = bv, last_at = ba;
+                }
+            }
             gs[g] = best;
         }
         __syncwarp();
@@ -106,7 +138,8 @@ __device__ __forceinline__ void moe_route_token(const float* zr, const float* __
 // One warp per token, logits given.  Shared memory per warp: s[E], choice[E], group[n_groups].
 __global__ void moe_route_kernel(const float* __restrict__ z, long z_stride, const float* __restrict__ correction,
                                  int* __restrict__ idx, float* __restrict__ weight, float* __restrict__ gate,
-                                 int n_tokens, int E, int top, int n_groups, int keep, float weight_scale, int extra) {
+                                 int n_tokens, int E, int top, int n_groups, int keep, float weight_scale, int extra,
+                                 int score_mode, int group_top) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float sm[];
@@ -115,13 +148,14 @@ __global__ void moe_route_kernel(const float* __restrict__ z, long z_stride, con
     if (t >= n_tokens) return;
     float* s = sm + (size_t)warp * (2 * E + n_groups);
     moe_route_token(z + (size_t)t * z_stride, correction, idx, weight, gate, s, s + E, s + 2 * E, t, E, top, n_groups, keep,
-                    weight_scale, extra, lane);
+                    weight_scale, extra, lane, score_mode, group_top);
 }
 
 extern "C" int bfi_moe_route(const float* z, long z_stride, const float* correction, int* idx, float* weight, float* gate,
                              int n_tokens, int E, int top, int n_groups, int keep, float weight_scale, int extra,
-                             cudaStream_t stream) {
+                             int score_mode, int group_top, cudaStream_t stream) {
     BFI_REQUIRE(E > 0 && top > 0 && top <= E, "moe_route: cannot choose %d of %d experts", top, E);
+    BFI_REQUIRE((score_mode == 0 || score_mode == 1) && group_top >= 1, "moe_route: unknown score mode or group rule");
     BFI_REQUIRE(n_groups > 0 && E % n_groups == 0 && keep > 0 && keep <= n_groups,
                 "moe_route: %d experts in %d groups, %d kept", E, n_groups, keep);
     BFI_REQUIRE((long)keep * (E / n_groups) >= top, "moe_route: %d groups of %d experts cannot give %d", keep, E / n_groups, top);
@@ -132,7 +166,7 @@ extern "C" int bfi_moe_route(const float* z, long z_stride, const float* correct
     const size_t smem = (size_t)warps * (2 * E + n_groups) * sizeof(float);
     BFI_REQUIRE(smem <= 48 * 1024, "moe_route: %d experts are too many for this kernel", E);
     bfi_launch(moe_route_kernel, dim3((n_tokens + warps - 1) / warps), dim3(32 * warps), smem, stream, z, z_stride, correction,
-               idx, weight, gate, n_tokens, E, top, n_groups, keep, weight_scale, extra);
+               idx, weight, gate, n_tokens, E, top, n_groups, keep, weight_scale, extra, score_mode, group_top);
     return bfi_check_launch("moe_route");
 }
 
@@ -187,7 +221,7 @@ __global__ void __launch_bounds__(256)
 moe_router_kernel(const T* __restrict__ h, long h_stride, const float* __restrict__ w_router,
                   const float* __restrict__ correction, const int* __restrict__ token_slot, int* __restrict__ idx,
                   float* __restrict__ weight, float* __restrict__ gate, int width, int E, int top, int n_groups, int keep,
-                  float weight_scale, int extra) {
+                  float weight_scale, int extra, int score_mode, int group_top) {
     pdl_trigger();
     extern __shared__ __align__(16) float sm[];
     float* hs = sm;                                // [width]
@@ -206,13 +240,15 @@ moe_router_kernel(const T* __restrict__ h, long h_stride, const float* __restric
     __syncthreads();
     if (warp == 0)
         moe_route_token(z, correction, idx, weight, gate, scratch, scratch + E, scratch + 2 * E, t, E, top, n_groups, keep,
-                        weight_scale, extra, lane);
+                        weight_scale, extra, lane, score_mode, group_top);
 }
 
 extern "C" int bfi_moe_router(const void* h, long h_stride, int dtype, const float* w_router, const float* correction,
                               const int* token_slot, int* idx, float* weight, float* gate, int n_tokens, int width, int E,
-                              int top, int n_groups, int keep, float weight_scale, int extra, cudaStream_t stream) {
+                              int top, int n_groups, int keep, float weight_scale, int extra, int score_mode, int group_top,
+                              cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "moe_router: unknown dtype code %d", dtype);
+    BFI_REQUIRE((score_mode == 0 || score_mode == 1) && group_top >= 1, "moe_router: unknown score mode or group rule");
     BFI_REQUIRE(E > 0 && top > 0 && top <= E && width > 0 && h_stride >= width, "moe_router: cannot choose %d of %d experts", top, E);
     BFI_REQUIRE(n_groups > 0 && E % n_groups == 0 && keep > 0 && keep <= n_groups,
                 "moe_router: %d experts in %d groups, %d kept", E, n_groups, keep);
@@ -226,12 +262,12 @@ extern "C" int bfi_moe_router(const void* h, long h_stride, int dtype, const flo
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_router_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_router_kernel<float>, dim3(n_tokens), dim3(256), smem, stream, (const float*)h, h_stride, w_router, correction,
-                       token_slot, idx, weight, gate, width, E, top, n_groups, keep, weight_scale, extra);
+                       token_slot, idx, weight, gate, width, E, top, n_groups, keep, weight_scale, extra, score_mode, group_top);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_router_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_router_kernel<bf16>, dim3(n_tokens), dim3(256), smem, stream, (const bf16*)h, h_stride, w_router, correction,
-                       token_slot, idx, weight, gate, width, E, top, n_groups, keep, weight_scale, extra);
+                       token_slot, idx, weight, gate, width, E, top, n_groups, keep, weight_scale, extra, score_mode, group_top);
     }
     if (e != cudaSuccess) return bfi_fail("moe_router: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     return bfi_check_launch("moe_router");
@@ -244,19 +280,26 @@ template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_gate_up_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__ w_gu,
                    const int* __restrict__ idx, const int* __restrict__ token_slot, T* __restrict__ act, int top,
-                   int width, int ff, int rows_per_block) {
+                   int width, int ff, int rows_per_block, int act_kind) {
     pdl_trigger();
     extern __shared__ __align__(16) float hs[];    // [width]
     const int pair = blockIdx.x;
     const int t = pair / top;
     if (token_slot[t] < 0) return;                 // padding row
     pdl_wait();
-    const int e = idx[pair];
+    const int e = idx != nullptr ? idx[pair] : 0;          // no choices: one expert that every token uses
     for (int j = threadIdx.x; j < width; j += blockDim.x) hs[j] = to_f32(h[(size_t)t * h_stride + j]);
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int r0 = blockIdx.y * rows_per_block;
     const int r1 = min(ff, r0 + rows_per_block);
+    if (act_kind == 1) {
+        for (int r = r0 + warp; r < r1; r += MOE_WARPS) {
+            const float u = fmaxf(warp_dot<T>(w_gu + ((size_t)e * ff + r) * width, hs, width, lane), 0.0f);
+            if (lane == 0) act[(size_t)pair * ff + r] = from_f32<T>(u * u);
+        }
+        return;
+    }
     for (int r = r0 + warp; r < r1; r += MOE_WARPS) {
         const size_t off = ((size_t)e * ff + r) * 2 * width;
         const float g = warp_dot<T>(w_gu + off, hs, width, lane);
@@ -267,8 +310,9 @@ moe_gate_up_kernel(const T* __restrict__ h, long h_stride, const T* __restrict__
 
 extern "C" int bfi_moe_gate_up(const void* h, long h_stride, int dtype, const void* w_gu,
                                const int* idx, const int* token_slot, void* act, int n_tokens, int top, int width, int ff,
-                               cudaStream_t stream) {
+                               int act_kind, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "moe_gate_up: unknown dtype code %d", dtype);
+    BFI_REQUIRE(act_kind == 0 || act_kind == 1, "moe_gate_up: unknown activation kind %d", act_kind);
     BFI_REQUIRE(top > 0 && width > 0 && ff > 0 && h_stride >= width, "moe_gate_up: bad sizes");
     if (n_tokens <= 0) return 0;
     const long pairs = (long)n_tokens * top;
@@ -287,12 +331,12 @@ extern "C" int bfi_moe_gate_up(const void* h, long h_stride, int dtype, const vo
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_gate_up_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_gate_up_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, stream, (const float*)h, h_stride,
-                       (const float*)w_gu, idx, token_slot, (float*)act, top, width, ff, rows_per_block);
+                       (const float*)w_gu, idx, token_slot, (float*)act, top, width, ff, rows_per_block, act_kind);
     } else {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_gate_up_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e == cudaSuccess)
             bfi_launch(moe_gate_up_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, stream, (const bf16*)h, h_stride,
-                       (const bf16*)w_gu, idx, token_slot, (bf16*)act, top, width, ff, rows_per_block);
+                       (const bf16*)w_gu, idx, token_slot, (bf16*)act, top, width, ff, rows_per_block, act_kind);
     }
     if (e != cudaSuccess) return bfi_fail("moe_gate_up: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
     return bfi_check_launch("moe_gate_up");
@@ -369,7 +413,7 @@ extern "C" int bfi_moe_down(const void* act, int dtype, const void* w_down, cons
 template <typename T>
 __global__ void moe_weigh_dense_kernel(T* __restrict__ act, long act_stride, const int* __restrict__ idx,
                                        const float* __restrict__ weight, const int* __restrict__ token_slot, int top, int E,
-                                       int ff, int tail, const float* __restrict__ gate) {
+                                       int ff, int tail, const float* __restrict__ gate, int act_kind) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ float comb[];                // [E] the token's weight of every expert
@@ -380,6 +424,21 @@ __global__ void moe_weigh_dense_kernel(T* __restrict__ act, long act_stride, con
     if (threadIdx.x < top) comb[idx[(size_t)t * top + threadIdx.x]] = weight[(size_t)t * top + threadIdx.x];
     __syncthreads();
     T* row = act + (size_t)t * act_stride;
+    if (act_kind == 1) {
+        // the row holds the up products themselves: relu(u)^2, rounded as the other way of computing
+        // rounds it, then the weight
+        for (int j = threadIdx.x; j < E * ff; j += blockDim.x) {
+            const float c = comb[j / ff];
+            const float u = fmaxf(to_f32(row[j]), 0.0f);
+            row[j] = c == 0.0f ? from_f32<T>(0.0f) : from_f32<T>(to_f32(from_f32<T>(u * u)) * c);
+        }
+        const float g = gate != nullptr ? gate[t] : 1.0f;
+        for (int j = E * ff + threadIdx.x; j < E * ff + tail; j += blockDim.x) {
+            const float u = fmaxf(to_f32(row[j]), 0.0f);
+            row[j] = gate != nullptr ? from_f32<T>(to_f32(from_f32<T>(u * u)) * g) : from_f32<T>(u * u);
+        }
+        return;
+    }
     for (int j = threadIdx.x; j < E * ff; j += blockDim.x) {
         const float c = comb[j / ff];
         row[j] = c == 0.0f ? from_f32<T>(0.0f) : from_f32<T>(to_f32(row[j]) * c);
@@ -392,8 +451,9 @@ __global__ void moe_weigh_dense_kernel(T* __restrict__ act, long act_stride, con
 
 extern "C" int bfi_moe_weigh_dense(void* act, long act_stride, int dtype, const int* idx, const float* weight,
                                    const int* token_slot, int n_tokens, int top, int E, int ff, int tail, const float* gate,
-                                   cudaStream_t stream) {
+                                   int act_kind, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "moe_weigh_dense: unknown dtype code %d", dtype);
+    BFI_REQUIRE(act_kind == 0 || act_kind == 1, "moe_weigh_dense: unknown activation kind %d", act_kind);
     BFI_REQUIRE(top > 0 && top <= 1024 && E > 0 && ff > 0 && tail >= 0 && act_stride >= (long)E * ff + tail,
                 "moe_weigh_dense: bad sizes");
     if (n_tokens <= 0) return 0;
@@ -402,10 +462,10 @@ extern "C" int bfi_moe_weigh_dense(void* act, long act_stride, int dtype, const 
     const int threads = top > 256 ? 1024 : 256;
     if (dtype == BFI_F32)
         bfi_launch(moe_weigh_dense_kernel<float>, dim3(n_tokens), dim3(threads), smem, stream, (float*)act, act_stride, idx, weight,
-                   token_slot, top, E, ff, tail, gate);
+                   token_slot, top, E, ff, tail, gate, act_kind);
     else
         bfi_launch(moe_weigh_dense_kernel<bf16>, dim3(n_tokens), dim3(threads), smem, stream, (bf16*)act, act_stride, idx, weight,
-                   token_slot, top, E, ff, tail, gate);
+                   token_slot, top, E, ff, tail, gate, act_kind);
     return bfi_check_launch("moe_weigh_dense");
 }
 

@@ -13,7 +13,7 @@ import torch
 
 from ..kernels import ops
 from ..kernels.linear import EPI_STORE, linear
-from ..parts.base import BLOCKS, NORMS, Block, ModelSpec, ParamSpec
+from ..parts.base import BLOCKS, INPUT_PARTS, NORMS, Block, ModelSpec, ParamSpec
 
 
 class Runtime:
@@ -37,6 +37,11 @@ def _validate_schedule(spec: ModelSpec) -> None:
 def expected_tensors(spec: ModelSpec) -> Dict[str, ParamSpec]:
     """Every checkpoint tensor the model wants: checkpoint name -> ParamSpec."""
     out: Dict[str, ParamSpec] = {spec.embedding_name: ParamSpec((spec.vocab_size, spec.width), "table")}
+    for j, (part_spec, names) in enumerate(spec.input_parts):
+        for local, ps in INPUT_PARTS.build(part_spec).all_param_specs().items():
+            if local not in names:
+                raise ValueError(f"input part {j}: no checkpoint name for parameter '{local}'")
+            out[names[local]] = ps
     for i, layer in enumerate(spec.layers):
         block = BLOCKS.build(layer.block)
         for local, ps in block.all_param_specs().items():
@@ -57,6 +62,7 @@ class Decoder:
         self.spec = spec
         self.runtime = runtime
         self.blocks: List[Block] = [BLOCKS.build(layer.block) for layer in spec.layers]
+        self.input_parts = [INPUT_PARTS.build(part_spec) for part_spec, _ in spec.input_parts]
         self.final_norm = NORMS.build(spec.final_norm)
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
@@ -69,12 +75,18 @@ class Decoder:
     def run_cache_of(self) -> List[Optional[int]]:
         return [r.cache_of for r in self.spec.schedule]
 
+    def model_needs(self) -> List[Any]:
+        """What the parts outside the layers keep per sequence, one entry per input part."""
+        return [p.cache_need() for p in self.input_parts]
+
     # ---- weights ---------------------------------------------------------------------
     def load(self, tensors: Dict[str, torch.Tensor], max_positions: int) -> None:
         """``tensors``: checkpoint name -> device tensor, as checked by the loader."""
         spec = self.spec
         self.embedding = tensors[spec.embedding_name]
         self.head = self.embedding if spec.head_name is None else tensors[spec.head_name]
+        for part, (_, names) in zip(self.input_parts, spec.input_parts):
+            part.load_all({name: tensors[ckpt] for name, ckpt in names.items() if ckpt in tensors}, self.runtime)
         for layer, block in zip(spec.layers, self.blocks):
             local = {name: tensors[ckpt] for name, ckpt in layer.names.items() if ckpt in tensors}
             block.load_all(local, self.runtime)
@@ -108,14 +120,15 @@ class Decoder:
         return total
 
     def graph_safe(self) -> bool:
-        return all(b.all_graph_safe() for b in self.blocks) and self.final_norm.all_graph_safe()
+        return all(b.all_graph_safe() for b in self.blocks) and self.final_norm.all_graph_safe() \
+            and all(p.all_graph_safe() for p in self.input_parts)
 
     def stages(self) -> List[tuple]:
         """A single-token step as stages that may (True) or may not be captured in a CUDA graph:
         ``("embed",)``, ``("runs", first, last)`` for schedule entries ``first .. last-1``, and
         ``("logits",)``, each with its flag; neighbours with the same flag are one stage.  A model
         whose parts are all graph-safe is one stage."""
-        ops: List[tuple] = [(True, ("embed",))]
+        ops: List[tuple] = [(all(p.all_graph_safe() for p in self.input_parts), ("embed",))]
         for i, run in enumerate(self.spec.schedule):
             ops.append((self.blocks[run.layer].all_graph_safe(), ("runs", i, i + 1)))
         ops.append((self.final_norm.all_graph_safe(), ("logits",)))
@@ -132,9 +145,14 @@ class Decoder:
         return out
 
     # ---- compute ---------------------------------------------------------------------
-    def embed(self, ctx) -> torch.Tensor:
+    def embed(self, ctx, cache=None) -> torch.Tensor:
+        """The embedded tokens, with what the input parts add; ``cache`` holds their per-sequence state."""
         x = ctx.rows("residual", self.spec.width, torch.float32)
         ops.embed_rows(self.embedding, ctx.token_ids[:ctx.n_tokens], x, ctx.status, float(self.spec.embedding_scale))
+        for j, part in enumerate(self.input_parts):
+            if cache is None:
+                raise RuntimeError("this model's input parts keep per-sequence state: embed() needs the cache")
+            part.forward(ctx, x, cache.model_cache(j))
         return x
 
     def run_layers(self, ctx, x: torch.Tensor, cache, first: int = 0, last: Optional[int] = None) -> None:

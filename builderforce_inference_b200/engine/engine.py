@@ -211,7 +211,7 @@ class _DecodeGraphs:
         x = ctx.rows("residual", engine.spec.width, torch.float32)
         for op in ops:
             if op[0] == "embed":
-                engine.decoder.embed(ctx)
+                engine.decoder.embed(ctx, engine.cache)
             elif op[0] == "runs":
                 engine.decoder.run_layers(ctx, x, engine.cache, op[1], op[2])
             else:
@@ -249,8 +249,9 @@ class Engine:
         self.stop_ids = tuple(spec.stop_ids)      # a loaded folder may add its generation_config.json's
         self.cache_plan = None
         if cache_bytes is not None:
-            self.cache_plan = plan_cache(self.decoder.run_needs(), self.decoder.run_cache_of(), int(cache_bytes),
-                                         2 if dtype == torch.bfloat16 else 4, cache_slots)
+            extra = self.decoder.model_needs()
+            self.cache_plan = plan_cache(self.decoder.run_needs() + extra, self.decoder.run_cache_of() + [None] * len(extra),
+                                         int(cache_bytes), 2 if dtype == torch.bfloat16 else 4, cache_slots)
             max_tokens = self.cache_plan.max_tokens
         limit = spec.max_positions if spec.max_positions > 0 else max_tokens
         self.max_seq_len = min(limit, max_seq_len) if max_seq_len else limit
@@ -258,7 +259,8 @@ class Engine:
                                       ((max_tokens + PAGE_TOKENS - 1) // PAGE_TOKENS) * PAGE_TOKENS))
         self.decoder.load(tensors, self.max_seq_len)
         self.cache = SequenceCache(self.decoder.run_needs(), self.decoder.run_cache_of(), max_tokens,
-                                   self.max_seq_len, dtype, device, initial_slots=max(1, int(cache_slots)))
+                                   self.max_seq_len, dtype, device, initial_slots=max(1, int(cache_slots)),
+                                   model_needs=self.decoder.model_needs())
         self.workspace = Workspace(device)
         self.status = torch.zeros(1, dtype=torch.int32, device=device)
         self.prefill_chunk_tokens = max(PAGE_TOKENS, int(prefill_chunk_tokens))
@@ -493,7 +495,7 @@ class Engine:
             meta = self._meta_buffer(n_tok, n_seq, len(rows))
             self._fill_meta(meta, tok, pos, slot_of, cu, n_tok, n_seq, p_slots, p_starts, rows)
             ctx = self._context_from_meta(meta, n_tok, n_seq, max(p_counts), (p_slots, p_starts, p_counts))
-            x = self.decoder.embed(ctx)
+            x = self.decoder.embed(ctx, self.cache)
             self.decoder.run_layers(ctx, x, self.cache)
             if rows:
                 row_idx = self._meta_slices(meta, n_tok, n_seq, len(rows))[7]
@@ -508,7 +510,7 @@ class Engine:
 
     # ---- one forward over a prepared context -----------------------------------------
     def _forward(self, ctx: StepContext, rows: torch.Tensor, logits: torch.Tensor) -> None:
-        x = self.decoder.embed(ctx)
+        x = self.decoder.embed(ctx, self.cache)
         self.decoder.run_layers(ctx, x, self.cache)
         self.decoder.logits(ctx, x, rows, logits[:rows.numel()])
 

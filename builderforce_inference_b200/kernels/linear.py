@@ -24,18 +24,23 @@ def _fast_ops():
     return _fast
 
 
-def _set_gate(fast: bool, alpha: float, limit: float, shift: float) -> None:
-    from ctypes import c_float
+GATE_SIGMOID, GATE_GELU_TANH = 0, 1      # kinds of the gated epilogue's activation
+
+
+def _set_gate(fast: bool, alpha: float, limit: float, shift: float, kind: int = GATE_SIGMOID) -> None:
+    from ctypes import c_float, c_int
 
     from .library import library
     for name in (("core", "fast") if fast else ("core",)):
-        library(name).lib.bfi_set_gate(c_float(alpha), c_float(limit), c_float(shift))
+        library(name).lib.bfi_set_gate_kind(c_int(kind), c_float(alpha), c_float(limit), c_float(shift))
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE, gate=None) -> None:
     """``gate``: with the gated epilogue, the activation's constants ``(alpha, limit, shift)``:
     ``g' * sigmoid(alpha * g') * (u' + shift)`` with gate and up clamped at ``limit`` (0: not
-    clamped); None is SiLU(gate) * up.  The kernels take them along as launch arguments."""
+    clamped); None is SiLU(gate) * up.  A fourth value names the activation's kind:
+    ``GATE_GELU_TANH`` is ``gelu_tanh(g) * u`` (the three constants are then unused).  The kernels
+    take them along as launch arguments."""
     fast = a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
     if gate is not None and epilogue == EPI_SWIGLU:
         _set_gate(fast, *gate)

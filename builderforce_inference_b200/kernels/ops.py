@@ -309,7 +309,8 @@ def attention_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv, cu_se
     ``h`` lies at ``q + t*q_stride + h*head_dim``.  ``out`` is ``[tokens, n_q*v_dim]``.  With
     ``sink`` (a number, or a float32 tensor with one per query head) the softmax's denominator
     carries ``exp(sink)`` beside the keys' terms.  The cache view says whether the values have a
-    size of their own and whether a token reads only its own chunk of positions."""
+    size of their own (or are the first values of the keys) and whether a token reads only its own
+    chunk of positions."""
     has_sink, sink_value, sinks = 0, 0.0, None
     if isinstance(sink, torch.Tensor):
         if sink.dtype != torch.float32 or not sink.is_contiguous() or sink.numel() != n_q or not sink.is_cuda:
@@ -326,10 +327,125 @@ def attention_paged(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv, cu_se
         raise KernelError("attention: q, output and cache must share a dtype")
     library("core").call(
         "bfi_attention_paged", _ptr(q), c_int(dtype_code(q.dtype)), c_long(q_stride), _ptr(out),
-        c_long(out.stride(0)), _ptr(kv.k), _ptr(kv.v), _ptr(kv.block_table), c_int(kv.block_table.stride(0)),
+        c_long(out.stride(0)), _ptr(kv.k), _ptr(None if kv.values_in_keys else kv.v), _ptr(kv.block_table),
+        c_int(kv.block_table.stride(0)),
         _ptr(cu_seqlens), _ptr(seq_slot), _ptr(seq_start), c_int(n_seqs), c_int(max_tokens), c_int(n_q),
         c_int(kv.n_kv_heads), c_int(kv.head_dim), c_int(kv.value_dim), c_int(kv.window or 0), c_int(kv.chunk or 0),
         c_float(scale), c_int(has_sink), c_float(sink_value), _ptr(sinks), _stream())
+
+
+def latent_prepare(proj: torch.Tensor, qa: torch.Tensor, n_heads: int, dim: int, rot_dim: int, rank: int, kv_off: int,
+                   norm_w: Optional[torch.Tensor], eps: float, rope_table: Optional[torch.Tensor], rot_used: int,
+                   token_pos: torch.Tensor, token_slot: torch.Tensor, kv, write_cache: bool,
+                   status: Optional[torch.Tensor] = None) -> None:
+    """Latent attention, per token: every query head's rotated part (``rot_dim`` values behind its
+    ``dim`` unrotated ones in ``proj``) turned by the position's angles and put at columns
+    ``rank .. rank + rot_dim`` of the head's row in ``qa`` ``[tokens, heads * (rank + rot_dim)]``; with
+    ``write_cache`` the down projection at column ``kv_off`` of ``proj`` becomes the token's cache
+    row: its first ``rank`` values RMS-normed with ``norm_w``, its last ``rot_dim`` turned.
+    ``rot_used`` of the rotated part's values turn (value i with value i + rot_used/2)."""
+    _need_cuda(proj, qa, norm_w, rope_table, token_pos, token_slot, status)
+    _rows_2d(proj, "projections")
+    _rows_2d(qa, "latent queries")
+    _i32(token_pos, "token positions")
+    _i32(token_slot, "token slots")
+    n = proj.shape[0]
+    if qa.dtype != proj.dtype or qa.shape != (n, n_heads * (rank + rot_dim)):
+        raise KernelError("latent_prepare: the query buffer must be [tokens, heads * (rank + rot_dim)] of the projections' dtype")
+    if proj.shape[1] < n_heads * (dim + rot_dim) or token_pos.numel() < n or token_slot.numel() < n:
+        raise KernelError("latent_prepare: a row is shorter than the heads, or the index arrays than the tokens")
+    positions = 0
+    if rot_used:
+        if rope_table is None or rope_table.dtype != torch.float32 or not rope_table.is_contiguous() or rope_table.dim() != 3 \
+                or rope_table.shape[1] != rot_used // 2 or rope_table.shape[2] != 2:
+            raise KernelError("rotation table must be contiguous float32 [positions, rot_dim/2, 2]")
+        positions = rope_table.shape[0]
+    k_pages = table = None
+    stride = 0
+    if write_cache:
+        if kv is None or kv.k.dtype != proj.dtype or kv.n_kv_heads != 1 or kv.head_dim != rank + rot_dim or not kv.k.is_contiguous():
+            raise KernelError("latent_prepare: the cache must hold one contiguous row of rank + rot_dim values per token")
+        if norm_w is None or norm_w.shape != (rank,) or not norm_w.is_contiguous() or proj.shape[1] < kv_off + rank + rot_dim:
+            raise KernelError("latent_prepare: writing the cache needs the latent's norm weight and the down projection's columns")
+        k_pages, table = kv.k, kv.block_table
+        stride = table.stride(0)
+    library("core").call(
+        "bfi_latent_prepare", _ptr(proj), c_int(dtype_code(proj.dtype)), c_long(proj.stride(0)), _ptr(qa), c_long(qa.stride(0)),
+        c_int(n), c_int(n_heads), c_int(dim), c_int(rot_dim), c_int(rank), c_int(kv_off), _ptr(norm_w),
+        c_int(0 if norm_w is None else dtype_code(norm_w.dtype)), c_float(eps), _ptr(rope_table if rot_used else None),
+        c_int(rot_used), c_int(positions), _ptr(token_pos), _ptr(token_slot), _ptr(k_pages), _ptr(table), c_int(stride),
+        c_int(1 if write_cache else 0), _ptr(status), _stream())
+
+
+def latent_absorb(proj: torch.Tensor, w_uk: torch.Tensor, qa: torch.Tensor, token_slot: torch.Tensor, n_heads: int, dim: int,
+                  rot_dim: int, rank: int) -> None:
+    """``qa[t, h, :rank] = W_uk_h^T q[t, h, :dim]`` with ``w_uk`` ``[heads * dim, rank]``: the unrotated
+    part of every query head taken into the latent space, where it meets the cached latents."""
+    _need_cuda(proj, w_uk, qa, token_slot)
+    _rows_2d(proj, "projections")
+    _rows_2d(qa, "latent queries")
+    _i32(token_slot, "token slots")
+    n = proj.shape[0]
+    if w_uk.shape != (n_heads * dim, rank) or not w_uk.is_contiguous():
+        raise KernelError(f"latent_absorb: the key matrices must be contiguous [{n_heads * dim}, {rank}]")
+    if qa.dtype != proj.dtype or qa.shape != (n, n_heads * (rank + rot_dim)) or proj.shape[1] < n_heads * (dim + rot_dim):
+        raise KernelError("latent_absorb: queries [tokens, heads * (dim + rot_dim)] in, [tokens, heads * (rank + rot_dim)] out")
+    library("core").call("bfi_latent_absorb", _ptr(proj), c_int(dtype_code(proj.dtype)), c_long(proj.stride(0)), _ptr(w_uk),
+                         c_int(dtype_code(w_uk.dtype)), _ptr(qa), c_long(qa.stride(0)), _ptr(token_slot), c_int(n),
+                         c_int(n_heads), c_int(dim), c_int(rot_dim), c_int(rank), _stream())
+
+
+def latent_expand(lat: torch.Tensor, w_uv: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor,
+                  token_slot: torch.Tensor, n_heads: int, v_dim: int, rank: int) -> None:
+    """``out[t, h] = (W_uv_h lat[t, h]) * sigmoid(gate[t, h])`` with ``w_uv`` ``[heads * v_dim, rank]``,
+    ``lat`` ``[tokens, heads * rank]`` (the attention's weighted sums of cached latents) and ``gate`` a
+    view ``[tokens, heads]`` of logits (None: no gate)."""
+    _need_cuda(lat, w_uv, gate, out, token_slot)
+    _rows_2d(lat, "latent outputs")
+    _rows_2d(out, "head outputs")
+    _i32(token_slot, "token slots")
+    n = lat.shape[0]
+    if w_uv.shape != (n_heads * v_dim, rank) or not w_uv.is_contiguous():
+        raise KernelError(f"latent_expand: the value matrices must be contiguous [{n_heads * v_dim}, {rank}]")
+    if lat.shape != (n, n_heads * rank) or out.shape != (n, n_heads * v_dim) or out.dtype != lat.dtype:
+        raise KernelError("latent_expand: [tokens, heads * rank] in, [tokens, heads * v_dim] out, of one dtype")
+    if gate is not None:
+        _rows_2d(gate, "gate logits")
+        if gate.shape != (n, n_heads) or gate.dtype != lat.dtype:
+            raise KernelError("latent_expand: the gate must be [tokens, heads] of the activations' dtype")
+    library("core").call("bfi_latent_expand", _ptr(lat), c_int(dtype_code(lat.dtype)), c_long(lat.stride(0)), _ptr(w_uv),
+                         c_int(dtype_code(w_uv.dtype)), _ptr(gate), c_long(0 if gate is None else gate.stride(0)), _ptr(out),
+                         c_long(out.stride(0)), _ptr(token_slot), c_int(n), c_int(n_heads), c_int(v_dim), c_int(rank), _stream())
+
+
+def bigram_add(table: torch.Tensor, ids: torch.Tensor, token_pos: torch.Tensor, token_slot: torch.Tensor,
+               last_token: torch.Tensor, x: torch.Tensor, mul_prev: int, mul_cur: int, vocab: int,
+               status: Optional[torch.Tensor] = None) -> None:
+    """``x[t] += table[(previous token * mul_prev + token * mul_cur) mod buckets]`` with ``table``
+    ``[buckets + 1, width]``; a token at position 0 takes the last row.  The previous token of a
+    sequence's first token in the step is ``last_token[slot]`` (int32 ``[slots, 1]``)."""
+    _need_cuda(table, ids, token_pos, token_slot, last_token, x, status)
+    _rows_2d(table, "bigram table")
+    for t, what in ((ids, "token ids"), (token_pos, "token positions"), (token_slot, "token slots"), (last_token, "last tokens")):
+        _i32(t, what)
+    n = x.shape[0]
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.shape[1] != table.shape[1] or not table.is_contiguous():
+        raise KernelError("bigram_add: the residual stream must be contiguous float32 [tokens, width], the table contiguous")
+    if ids.numel() < n or token_pos.numel() < n or token_slot.numel() < n or table.shape[0] < 2:
+        raise KernelError("bigram_add: index arrays shorter than the tokens, or a table without buckets")
+    library("core").call("bfi_bigram_add", _ptr(table), c_int(dtype_code(table.dtype)), _ptr(ids), _ptr(token_pos),
+                         _ptr(token_slot), _ptr(last_token), _ptr(x), c_int(n), c_int(x.shape[1]), c_int(table.shape[0] - 1),
+                         c_long(int(mul_prev)), c_long(int(mul_cur)), c_int(vocab), _ptr(status), _stream())
+
+
+def keep_last_tokens(ids: torch.Tensor, cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, last_token: torch.Tensor,
+                     n_seqs: int) -> None:
+    """``last_token[slot] = `` the last token id each sequence brings in this step."""
+    _need_cuda(ids, cu_seqlens, seq_slot, last_token)
+    for t, what in ((ids, "token ids"), (cu_seqlens, "cu_seqlens"), (seq_slot, "sequence slots"), (last_token, "last tokens")):
+        _i32(t, what)
+    library("core").call("bfi_keep_last_tokens", _ptr(ids), _ptr(cu_seqlens), _ptr(seq_slot), _ptr(last_token), c_int(n_seqs),
+                         _stream())
 
 
 def _f32_vector(t: Optional[torch.Tensor], n: int, what: str) -> None:
@@ -500,11 +616,17 @@ def gated_group_norm(x: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: 
                          c_int(gate_act), c_float(eps), _stream())
 
 
+SCORE_SOFTMAX, SCORE_SIGMOID = 0, 1
+EXPERT_GATED_SILU, EXPERT_RELU_SQUARED = 0, 1
+
+
 def moe_route(z: torch.Tensor, n_experts: int, correction: Optional[torch.Tensor], idx: torch.Tensor,
               weight: torch.Tensor, top: int, n_groups: int = 1, keep: int = 1, weight_scale: float = 1.0,
-              gate: Optional[torch.Tensor] = None) -> None:
-    """The router's decision per token from float32 logits ``z[:, :n_experts]``: softmax, choice
-    scores ``s + correction``, the ``keep`` best of ``n_groups`` groups, the ``top`` best experts of
+              gate: Optional[torch.Tensor] = None, score: int = SCORE_SOFTMAX, group_top: int = 1) -> None:
+    """The router's decision per token from float32 logits ``z[:, :n_experts]``: scores ``s`` (the
+    softmax over the experts, or with ``SCORE_SIGMOID`` each expert's own sigmoid), choice
+    scores ``s + correction``, the ``keep`` best of ``n_groups`` groups (a group counts by the sum of
+    its ``group_top`` largest choice scores), the ``top`` best experts of
     those; ``idx`` int32 and ``weight`` float32 ``[tokens, top]`` (the chosen ``s`` times
     ``weight_scale``).  With ``gate`` (float32 ``[tokens]``): ``sigmoid(z[:, n_experts])``."""
     _need_cuda(z, correction, idx, weight, gate)
@@ -520,12 +642,13 @@ def moe_route(z: torch.Tensor, n_experts: int, correction: Optional[torch.Tensor
         raise KernelError("moe_route: the gate must be contiguous float32 [tokens]")
     library("core").call("bfi_moe_route", _ptr(z), c_long(z.stride(0)), _ptr(correction), _ptr(idx), _ptr(weight), _ptr(gate),
                          c_int(n), c_int(n_experts), c_int(top), c_int(n_groups), c_int(keep), c_float(weight_scale),
-                         c_int(0 if gate is None else 1), _stream())
+                         c_int(0 if gate is None else 1), c_int(score), c_int(group_top), _stream())
 
 
 def moe_router(h: torch.Tensor, w_router: torch.Tensor, n_experts: int, correction: Optional[torch.Tensor],
                token_slot: torch.Tensor, idx: torch.Tensor, weight: torch.Tensor, top: int, n_groups: int = 1, keep: int = 1,
-               weight_scale: float = 1.0, gate: Optional[torch.Tensor] = None) -> None:
+               weight_scale: float = 1.0, gate: Optional[torch.Tensor] = None, score: int = SCORE_SOFTMAX,
+               group_top: int = 1) -> None:
     """``moe_route`` with the logits made in the same kernel: ``z = w_router h`` with ``w_router``
     float32 ``[n_experts (+ 1), width]`` (the extra row is the gate's, wanted with ``gate``)."""
     _need_cuda(h, w_router, correction, token_slot, idx, weight, gate)
@@ -544,27 +667,33 @@ def moe_router(h: torch.Tensor, w_router: torch.Tensor, n_experts: int, correcti
     library("core").call("bfi_moe_router", _ptr(h), c_long(h.stride(0)), c_int(dtype_code(h.dtype)), _ptr(w_router),
                          _ptr(correction), _ptr(token_slot), _ptr(idx), _ptr(weight), _ptr(gate), c_int(n), c_int(width),
                          c_int(n_experts), c_int(top), c_int(n_groups), c_int(keep), c_float(weight_scale),
-                         c_int(0 if gate is None else 1), _stream())
+                         c_int(0 if gate is None else 1), c_int(score), c_int(group_top), _stream())
 
 
 def moe_gate_up(h: torch.Tensor, w_gu: torch.Tensor, n_experts: int, idx: torch.Tensor, token_slot: torch.Tensor,
-                act: torch.Tensor) -> None:
+                act: torch.Tensor, kind: int = EXPERT_GATED_SILU) -> None:
     """``act[t, k] = silu(gate_e h_t) * (up_e h_t)`` with ``e = idx[t, k]``; ``w_gu`` is
     ``[experts * 2 * ff, width]`` with expert e's gate row j at row ``2 (e ff + j)`` and its up row
-    after it, ``act`` ``[tokens * top, ff]``."""
+    after it, ``act`` ``[tokens * top, ff]``.  ``EXPERT_RELU_SQUARED``: ``act[t, k] = relu(up_e h_t)^2``
+    with ``w_gu`` ``[experts * ff, width]``, the experts' up matrices one after the other.  ``idx``
+    None (with one expert): every token uses that expert."""
     _need_cuda(h, w_gu, idx, token_slot, act)
     _rows_2d(h, "feed-forward input")
     n, width = h.shape
-    top = idx.shape[1]
-    ff = w_gu.shape[0] // (2 * n_experts)
-    if w_gu.dim() != 2 or w_gu.shape != (n_experts * 2 * ff, width) or not w_gu.is_contiguous() or w_gu.dtype != h.dtype:
-        raise KernelError("moe_gate_up: expert weights must be contiguous [experts * 2 * ff, width] of the input's dtype")
+    if idx is None and n_experts != 1:
+        raise KernelError("moe_gate_up: without choices there is one expert")
+    top = 1 if idx is None else idx.shape[1]
+    per = 1 if kind == EXPERT_RELU_SQUARED else 2
+    ff = w_gu.shape[0] // (per * n_experts)
+    if w_gu.dim() != 2 or w_gu.shape != (n_experts * per * ff, width) or not w_gu.is_contiguous() or w_gu.dtype != h.dtype:
+        raise KernelError(f"moe_gate_up: expert weights must be contiguous [experts * {per} * ff, width] of the input's dtype")
     if act.dtype != h.dtype or not act.is_contiguous() or act.shape != (n * top, ff):
         raise KernelError("moe_gate_up: the output must be contiguous [tokens * top, ff] of the input's dtype")
     _i32(idx, "expert choices")
     _i32(token_slot, "token slots")
     library("core").call("bfi_moe_gate_up", _ptr(h), c_long(h.stride(0)), c_int(dtype_code(h.dtype)), _ptr(w_gu),
-                         _ptr(idx), _ptr(token_slot), _ptr(act), c_int(n), c_int(top), c_int(width), c_int(ff), _stream())
+                         _ptr(idx), _ptr(token_slot), _ptr(act), c_int(n), c_int(top), c_int(width), c_int(ff), c_int(kind),
+                         _stream())
 
 
 def moe_down(act: torch.Tensor, w_down: torch.Tensor, n_experts: int, idx: torch.Tensor, weight: torch.Tensor,
@@ -594,10 +723,13 @@ def moe_down(act: torch.Tensor, w_down: torch.Tensor, n_experts: int, idx: torch
 
 
 def moe_weigh_dense(act: torch.Tensor, n_experts: int, idx: torch.Tensor, weight: torch.Tensor,
-                    token_slot: torch.Tensor, tail: int = 0, gate: Optional[torch.Tensor] = None) -> None:
+                    token_slot: torch.Tensor, tail: int = 0, gate: Optional[torch.Tensor] = None,
+                    kind: int = EXPERT_GATED_SILU) -> None:
     """``act[t, e ff + j] *= (weight of expert e for token t, 0 if it was not chosen)`` over
     activations ``[tokens, experts * ff + tail]`` that the dense product computed for every expert;
-    the last ``tail`` columns (an expert every token uses) are multiplied by ``gate[t]``."""
+    the last ``tail`` columns (an expert every token uses) are multiplied by ``gate[t]`` (None: 1).
+    ``EXPERT_RELU_SQUARED``: the columns hold the up products themselves and become ``relu(u)^2``
+    here, before their weight."""
     _need_cuda(act, idx, weight, token_slot, gate)
     _rows_2d(act, "dense expert activations")
     _i32(idx, "expert choices")
@@ -607,11 +739,13 @@ def moe_weigh_dense(act: torch.Tensor, n_experts: int, idx: torch.Tensor, weight
     if act.shape[0] != n or tail < 0 or routed <= 0 or routed % n_experts != 0 or weight.dtype != torch.float32 \
             or not weight.is_contiguous() or weight.shape != (n, top):
         raise KernelError("moe_weigh_dense: activations [tokens, experts * ff + tail], weights float32 [tokens, top]")
-    if tail and (gate is None or gate.dtype != torch.float32 or not gate.is_contiguous() or gate.numel() < n):
+    if tail and kind == EXPERT_GATED_SILU and gate is None:
         raise KernelError("moe_weigh_dense: the tail needs one float32 gate per token")
+    if gate is not None and (gate.dtype != torch.float32 or not gate.is_contiguous() or gate.numel() < n):
+        raise KernelError("moe_weigh_dense: the gate must be contiguous float32 with one value per token")
     library("core").call("bfi_moe_weigh_dense", _ptr(act), c_long(act.stride(0)), c_int(dtype_code(act.dtype)), _ptr(idx),
                          _ptr(weight), _ptr(token_slot), c_int(n), c_int(top), c_int(n_experts), c_int(routed // n_experts),
-                         c_int(tail), _ptr(gate), _stream())
+                         c_int(tail), _ptr(gate), c_int(kind), _stream())
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, epilogue: int = EPI_STORE) -> None:

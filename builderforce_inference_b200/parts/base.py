@@ -24,6 +24,9 @@ Contracts (all tensors live on the GPU):
     ``apply(ctx, q, k)``.
 ``Block.forward(ctx, residual, run)``
     arranges norms, mixer and feed-forward around the residual stream.
+``InputPart.forward(ctx, x, run)``
+    adds to the embedded tokens before the first block (a second embedding, say); ``run`` carries
+    the per-sequence state it asked for.
 
 Every part lists the tensors it wants in ``param_specs()`` under local names; the model's
 ``names`` maps them to checkpoint tensor names.  ``load(tensors)`` receives them on the device,
@@ -58,17 +61,24 @@ class KVNeed:
     """A mixer that keeps keys and values of earlier tokens: all of them, a window (the last
     ``window`` positions), or the current chunk (the positions of the token's own block of ``chunk``
     consecutive positions, blocks counted from position 0).  ``v_dim`` is the size of a value head
-    where it differs from the keys' ``head_dim``."""
+    where it differs from the keys' ``head_dim``.  ``values_in_keys``: a token's value is the first
+    ``v_dim`` values of its key, so only keys are stored (a latent attention's cache row)."""
 
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_dim: Optional[int] = None
     chunk: Optional[int] = None
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
         return self.head_dim if self.v_dim is None else self.v_dim
+
+    @property
+    def stored_per_head(self) -> int:
+        """Values one token keeps per key/value head."""
+        return self.head_dim if self.values_in_keys else self.head_dim + self.value_dim
 
 
 @dataclass(frozen=True)
@@ -118,6 +128,18 @@ class Part:
 
 class Norm(Part):
     def forward(self, ctx, x, rows=None):
+        raise NotImplementedError
+
+
+class InputPart(Part):
+    """Something added to the residual stream right after the token embedding.  It may keep a
+    fixed-size state per sequence (``cache_need``), which it finds in ``run.entries``."""
+
+    def cache_need(self):
+        return None
+
+    def forward(self, ctx, x, run) -> None:
+        """Adds into ``x`` (float32 ``[tokens, width]``) in place."""
         raise NotImplementedError
 
 
@@ -203,6 +225,7 @@ class Registry:
 
 
 NORMS = Registry("norm")
+INPUT_PARTS = Registry("input part")
 POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
@@ -243,3 +266,5 @@ class ModelSpec:
     stop_ids: Tuple[int, ...] = ()
     embedding_scale: float = 1.0       # the embedding rows are multiplied by it; the tied head is not
     logit_scale: float = 1.0           # the logits are multiplied by it
+    # parts added to the embedded tokens, each with the checkpoint names of its tensors: (PartSpec, names)
+    input_parts: Sequence[Tuple[PartSpec, Mapping[str, str]]] = ()

@@ -1,7 +1,8 @@
 """Residual blocks.  The residual stream stays float32 in every run dtype; the adds happen inside
 the mixer's and the feed-forward's last matrix product.
 
-``prenorm``   ``x += mixer(norm1(x)); x += ffn(norm2(x))`` (crates/bfi-models/src/qwen3.rs:217-250).
+``prenorm``   ``x += mixer(norm1(x)); x += ffn(norm2(x))`` (crates/bfi-models/src/qwen3.rs:217-250); the
+              feed-forward (with its norm) may be absent.
 ``parallel``  one norm, both sublayers read its output: ``h = norm1(x); x += mixer(h) + ffn(h)``;
               the feed-forward may be absent.
 ``sandwich``  a norm before and after each sublayer: ``x += norm1b(mixer(norm1(x)));
@@ -19,14 +20,19 @@ from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, PartSpec
 class PreNormBlock(Block):
     graph_safe = True
 
-    def __init__(self, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, ffn: PartSpec):
+    def __init__(self, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec = None, ffn: PartSpec = None):
+        if (ffn is None) != (norm2 is None):
+            raise ValueError("a pre-norm block has a feed-forward with its norm, or neither")
         self.norm1 = NORMS.build(norm1)
         self._mixer = MIXERS.build(mixer)
-        self.norm2 = NORMS.build(norm2)
-        self.ffn = FEED_FORWARDS.build(ffn)
+        self.norm2 = NORMS.build(norm2) if ffn is not None else None
+        self.ffn = FEED_FORWARDS.build(ffn) if ffn is not None else None
 
     def children(self):
-        return {"norm1": self.norm1, "mixer": self._mixer, "norm2": self.norm2, "ffn": self.ffn}
+        out = {"norm1": self.norm1, "mixer": self._mixer}
+        if self.ffn is not None:
+            out.update({"norm2": self.norm2, "ffn": self.ffn})
+        return out
 
     def mixer(self):
         return self._mixer
@@ -34,6 +40,8 @@ class PreNormBlock(Block):
     def forward(self, ctx, residual, run) -> None:
         h = self.norm1.forward(ctx, residual)
         self._mixer.forward(ctx, h, residual, run)
+        if self.ffn is None:
+            return
         h = self.norm2.forward(ctx, residual)
         self.ffn.forward(ctx, h, residual)
 

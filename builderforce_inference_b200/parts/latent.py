@@ -1,0 +1,141 @@
+"""Latent attention, as a mixer: keys and values of all heads are made from one small vector per
+token, and only that vector is cached.
+
+Per token with input ``h``: the queries ``q = W_q h``, head by head ``[dim unrotated | rot_dim
+rotated]``; the down projection ``W_dkv h`` whose first ``kv_rank`` values, RMS-normed, are the
+latent ``c`` and whose last ``rot_dim`` values are one rotated key part that all heads share.  Head
+``a``'s unrotated key is ``W_uk_a c``, its value ``W_uv_a c``; its score against a token is
+``(q_a^n . k_a^n + q_a^r . k^r) * scale``; the softmax is causal and may carry a learned sink per
+head in its denominator; head ``a``'s output may be multiplied by ``sigmoid(W_g h)_a``; ``W_o`` acts
+on the concatenated heads.
+
+Here the attention runs in the latent space.  Since ``q_a^n . W_uk_a c = (W_uk_a^T q_a^n) . c`` and
+``sum_j p_j W_uv_a c_j = W_uv_a sum_j p_j c_j``, every query head becomes
+``[W_uk_a^T q_a^n | rot(q_a^r)]`` (``kv_rank + rot_dim`` values), all heads read the same cached
+rows ``[c | rot(k^r)]`` as ONE key/value head whose values are the first ``kv_rank`` values of its
+keys, and ``W_uv_a`` takes head ``a``'s weighted sum of latents to its ``v_dim`` outputs.  The cache
+holds ``kv_rank + rot_dim`` values per token and nothing is expanded per cached token, whatever
+the number of heads; a layer without a down projection of its own (``own_kv`` false) reads the
+rows another layer's run has written, with its own ``W_uk`` and ``W_uv``.
+
+Launches: one product for queries, gate logits and down projection together; ``latent_prepare``
+(rotations, the latent's norm, the cache write); ``latent_absorb``; the paged attention;
+``latent_expand`` (``W_uv`` and the gate); the output product, which adds into the residual stream.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import ops
+from ..kernels.linear import EPI_ACCUMULATE, EPI_STORE, linear
+from .base import MIXERS, POSITION_ENCODINGS, KVNeed, Mixer, ParamSpec, PartSpec
+
+
+@MIXERS.register("latent_attention")
+class LatentAttention(Mixer):
+    graph_safe = True
+
+    def __init__(self, width: int, n_heads: int, dim: int, rot_dim: int, v_dim: int, kv_rank: int,
+                 position: Optional[PartSpec] = None, eps: float = 1e-6, scale: Optional[float] = None,
+                 own_kv: bool = True, sink=None, gate: bool = False):
+        if n_heads < 1 or dim < 1 or rot_dim < 0 or v_dim < 1 or kv_rank < 1:
+            raise ValueError(f"latent attention: bad sizes heads={n_heads} dim={dim} rot_dim={rot_dim} v_dim={v_dim} "
+                             f"kv_rank={kv_rank}")
+        if (kv_rank + rot_dim) % 2 != 0 or kv_rank + rot_dim > 512:
+            raise ValueError(f"latent attention: kv_rank + rot_dim = {kv_rank + rot_dim} must be even and at most 512")
+        if not (sink is None or sink == "learned" or isinstance(sink, (int, float))):
+            raise ValueError(f"sink must be a number or 'learned', got {sink!r}")
+        self.width, self.n_heads, self.dim, self.rot_dim = int(width), int(n_heads), int(dim), int(rot_dim)
+        self.v_dim, self.kv_rank, self.eps = int(v_dim), int(kv_rank), float(eps)
+        self.scale = float(scale) if scale is not None else (dim + rot_dim) ** -0.5
+        self.own_kv, self.has_gate = bool(own_kv), bool(gate)
+        self.learned_sink = sink == "learned"
+        self.sink = None if sink is None or self.learned_sink else float(sink)
+        self.position = POSITION_ENCODINGS.build(position) if position is not None \
+            else POSITION_ENCODINGS.build(PartSpec("none"))
+        rot_used = getattr(self.position, "rot_dim", 0)
+        if rot_used > self.rot_dim:
+            raise ValueError(f"latent attention: {rot_used} rotated values do not fit a rotated part of {self.rot_dim}")
+        if getattr(self.position, "pairing", "half") != "half":
+            raise ValueError("latent attention rotates with the 'half' pairing")
+
+    def children(self):
+        return {"position": self.position}
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        w, a = self.width, self.n_heads
+        specs = {"q_proj": ParamSpec((a * (self.dim + self.rot_dim), w)),
+                 "uk_proj": ParamSpec((a * self.dim, self.kv_rank)),
+                 "uv_proj": ParamSpec((a * self.v_dim, self.kv_rank)),
+                 "o_proj": ParamSpec((w, a * self.v_dim))}
+        if self.own_kv:
+            specs["dkv_proj"] = ParamSpec((self.kv_rank + self.rot_dim, w))
+            specs["dkv_norm"] = ParamSpec((self.kv_rank,), "norm")
+        if self.learned_sink:
+            specs["sink"] = ParamSpec((a,), "matrix")
+        if self.has_gate:
+            specs["g_proj"] = ParamSpec((a, w))
+        return specs
+
+    def cache_need(self):
+        return KVNeed(1, self.kv_rank + self.rot_dim, v_dim=self.kv_rank, values_in_keys=True)
+
+    def prepare(self, runtime, max_positions: int) -> None:
+        self.position.prepare(runtime, max_positions)
+
+    def load(self, tensors, runtime) -> None:
+        # one product makes the queries, the gate logits and the down projection: rows in that order
+        mats = [tensors["q_proj"]]
+        self.gate_off = self.kv_off = mats[0].shape[0]
+        if self.has_gate:
+            mats.append(tensors["g_proj"])
+            self.kv_off += self.n_heads
+        # the down projection's columns start at a multiple of 8 values (16 bytes in either dtype)
+        pad = (-self.kv_off) % 8 if self.own_kv else 0
+        if pad:
+            mats.append(torch.zeros((pad, self.width), dtype=mats[0].dtype, device=mats[0].device))
+            self.kv_off += pad
+        if self.own_kv:
+            mats.append(tensors["dkv_proj"])
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.float() for m in mats]
+        self.w_in = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
+        self.w_uk = tensors["uk_proj"].contiguous()
+        self.w_uv = tensors["uv_proj"].contiguous()
+        self.w_o = tensors["o_proj"]
+        self.dkv_norm = tensors["dkv_norm"].contiguous() if self.own_kv else None
+        self.sinks = tensors["sink"].float().contiguous() if self.learned_sink else None
+
+    def forward(self, ctx, h, residual, run) -> None:
+        self._run(ctx, h, residual, run, EPI_ACCUMULATE)
+
+    def forward_store(self, ctx, h, out, run) -> None:
+        self._run(ctx, h, out, run, EPI_STORE)
+
+    def _run(self, ctx, h, target, run, epilogue) -> None:
+        kv = run.kv
+        if kv is None:
+            raise RuntimeError("latent attention needs a cache for its run")
+        if run.writes_cache != self.own_kv:
+            raise RuntimeError("a latent attention layer writes the cache exactly when it has a down projection")
+        a, r, rd = self.n_heads, self.kv_rank, self.rot_dim
+        proj = ctx.rows("latent.proj", self.w_in.shape[0])
+        linear(h, self.w_in, proj, EPI_STORE)
+        table, rot_used = self.position.fused_rotary()
+        qa = ctx.rows("latent.q", a * (r + rd))
+        ops.latent_prepare(proj, qa, a, self.dim, rd, r, self.kv_off, self.dkv_norm, self.eps, table, rot_used,
+                           ctx.token_pos, ctx.token_slot, kv, run.writes_cache, ctx.status)
+        ops.latent_absorb(proj, self.w_uk, qa, ctx.token_slot, a, self.dim, rd, r)
+        lat = ctx.rows("latent.out", a * r)
+        self.attend(ctx, qa, lat, kv)
+        out = ctx.rows("attn.out", a * self.v_dim)
+        gate = proj[:, self.gate_off:self.gate_off + a] if self.has_gate else None
+        ops.latent_expand(lat, self.w_uv, gate, out, ctx.token_slot, a, self.v_dim, r)
+        linear(out, self.w_o, target, epilogue)
+
+    def attend(self, ctx, qa, lat, kv) -> None:
+        sink = self.sinks if self.learned_sink else self.sink
+        ops.attention_paged(qa, qa.stride(0), lat, kv, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
+                            ctx.n_seqs, ctx.max_seq_tokens, self.n_heads, self.scale, sink)

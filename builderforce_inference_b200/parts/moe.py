@@ -21,6 +21,13 @@ stands behind the routed ones in both matrices and is weighed by its gate there,
 two products and one kernel between them.  In the other way the shared expert runs through dense
 products of its own.  Nothing here reads a choice back to the host, so a step through
 this part can be captured in a graph.
+
+Variants, each a parameter: ``score`` ``"sigmoid"`` (``s = sigmoid(z)``, every expert by itself, instead
+of the softmax); ``group_top`` (a group counts by the sum of its ``group_top`` best choice scores
+instead of the best one); ``correction`` false (no stored vector: experts are chosen by ``s``);
+``expert`` ``"relu_squared"`` (an expert is ``W_down relu(W_up h)^2``, without a gate matrix: the up
+matrices of all experts are one matrix, and in the dense way the activation is applied by the
+kernel that weighs); ``shared_gate`` false (the shared expert is added as it is).
 """
 from __future__ import annotations
 
@@ -41,7 +48,8 @@ class RoutedMLP(FeedForward):
     graph_safe = True
 
     def __init__(self, width: int, n_experts: int, top: int, inner: int, n_groups: int = 1, keep_groups: int = 1,
-                 shared_inner: Optional[int] = None, correction: bool = True, weight_scale: float = 1.0):
+                 shared_inner: Optional[int] = None, correction: bool = True, weight_scale: float = 1.0,
+                 score: str = "softmax", group_top: int = 1, expert: str = "gated_silu", shared_gate: bool = True):
         if n_experts < 1 or not 1 <= top <= n_experts or inner < 1:
             raise ValueError(f"routed feed-forward: bad sizes experts={n_experts} top={top} inner={inner}")
         if n_groups < 1 or n_experts % n_groups != 0 or not 1 <= keep_groups <= n_groups:
@@ -52,6 +60,13 @@ class RoutedMLP(FeedForward):
         self.n_groups, self.keep_groups = int(n_groups), int(keep_groups)
         self.shared_inner = None if shared_inner is None else int(shared_inner)
         self.has_correction, self.weight_scale = bool(correction), float(weight_scale)
+        if score not in ("softmax", "sigmoid") or expert not in ("gated_silu", "relu_squared") or group_top < 1:
+            raise ValueError(f"routed feed-forward: score {score!r}, expert {expert!r}, group_top {group_top}")
+        self.score = ops.SCORE_SIGMOID if score == "sigmoid" else ops.SCORE_SOFTMAX
+        self.group_top = int(group_top)
+        self.gated = expert == "gated_silu"
+        self.kind = ops.EXPERT_GATED_SILU if self.gated else ops.EXPERT_RELU_SQUARED
+        self.shared_gate = bool(shared_gate) and self.shared_inner is not None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         w = self.width
@@ -59,39 +74,48 @@ class RoutedMLP(FeedForward):
         if self.has_correction:
             specs["correction"] = ParamSpec((self.n_experts,))
         for e in range(self.n_experts):
-            specs[f"experts.{e}.gate_proj"] = ParamSpec((self.inner, w))
+            if self.gated:
+                specs[f"experts.{e}.gate_proj"] = ParamSpec((self.inner, w))
             specs[f"experts.{e}.up_proj"] = ParamSpec((self.inner, w))
             specs[f"experts.{e}.down_proj"] = ParamSpec((w, self.inner))
         if self.shared_inner is not None:
-            specs["shared.gate_proj"] = ParamSpec((self.shared_inner, w))
+            if self.gated:
+                specs["shared.gate_proj"] = ParamSpec((self.shared_inner, w))
             specs["shared.up_proj"] = ParamSpec((self.shared_inner, w))
             specs["shared.down_proj"] = ParamSpec((w, self.shared_inner))
-            specs["shared.gate"] = ParamSpec((1, w))
+            if self.shared_gate:
+                specs["shared.gate"] = ParamSpec((1, w))
         return specs
 
     def load(self, tensors, runtime) -> None:
-        mats = [tensors[f"experts.{e}.{kind}"] for e in range(self.n_experts) for kind in ("gate_proj", "up_proj", "down_proj")]
+        kinds = ("gate_proj", "up_proj", "down_proj") if self.gated else ("up_proj", "down_proj")
+        per = len(kinds)
+        mats = [tensors[f"experts.{e}.{kind}"] for e in range(self.n_experts) for kind in kinds]
+        if self.shared_inner is not None:
+            mats += [tensors[f"shared.{kind}"] for kind in kinds]
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
-        gu = [torch.stack([mats[3 * e], mats[3 * e + 1]], dim=1).reshape(2 * self.inner, self.width) for e in range(self.n_experts)]
-        downs = [mats[3 * e + 2] for e in range(self.n_experts)]
+        n_all = self.n_experts + (1 if self.shared_inner is not None else 0)
+        # gate and up rows interleaved, or the up rows alone; the shared expert stands behind the routed
+        # ones in both matrices, so the dense way is two products for all of them; the other way reads
+        # it through views (and its own down matrix)
+        if self.gated:
+            gu = [torch.stack([mats[per * e], mats[per * e + 1]], dim=1).reshape(-1, self.width) for e in range(n_all)]
+        else:
+            gu = [mats[per * e] for e in range(n_all)]
+        downs = [mats[per * e + per - 1] for e in range(n_all)]
         rows = [tensors["router"].float()]
-        if self.shared_inner is not None:
-            # the shared expert stands behind the routed ones in both matrices, so the dense way is two
-            # products for all of them; the other way reads it through views (and its own down matrix)
+        if self.shared_gate:
             rows.append(tensors["shared.gate"].float())
-            g, u, dn = tensors["shared.gate_proj"], tensors["shared.up_proj"], tensors["shared.down_proj"]
-            if len({g.dtype, u.dtype, dn.dtype, gu[0].dtype}) > 1:
-                g, u, dn, gu, downs = g.float(), u.float(), dn.float(), [m.float() for m in gu], [m.float() for m in downs]
-            gu.append(torch.stack([g, u], dim=1).reshape(2 * self.shared_inner, self.width))
-            downs.append(dn)
-            self.ws_down = dn.contiguous()
-        self.w_gu_all = torch.cat(gu, dim=0).contiguous()                  # [(E * ff + shared) * 2, width]
+        if self.shared_inner is not None:
+            self.ws_down = downs[-1].contiguous()
+        self.w_gu_all = torch.cat(gu, dim=0).contiguous()                  # [(E * ff + shared) * (2 | 1), width]
         self.w_down_all = torch.cat(downs, dim=1).contiguous()             # [width, E * ff + shared]
         routed = self.n_experts * self.inner
-        self.w_gu = self.w_gu_all[:2 * routed]                             # [E * 2 * ff, width]
+        rows_per = 2 if self.gated else 1
+        self.w_gu = self.w_gu_all[:rows_per * routed]                      # [E * (2 | 1) * ff, width]
         self.w_down = self.w_down_all[:, :routed]                          # [width, E * ff], rows of the wider matrix
-        self.routed_rows = 2 * routed                                      # the shared expert's gate/up rows follow
+        self.routed_rows = rows_per * routed                               # the shared expert's rows follow
         self.w_router = torch.cat(rows, dim=0).contiguous()                # float32: the logits are float32 sums
         self.correction = tensors["correction"].float().contiguous() if self.has_correction else None
 
@@ -106,23 +130,26 @@ class RoutedMLP(FeedForward):
         shared = self.shared_inner is not None
         idx = ctx.rows("moe.idx", self.top, torch.int32)
         wts = ctx.rows("moe.weight", self.top, torch.float32)
-        gate = ctx.rows("moe.gate", 1, torch.float32).view(-1) if shared else None
+        gate = ctx.rows("moe.gate", 1, torch.float32).view(-1) if self.shared_gate else None
         ops.moe_router(h, self.w_router, self.n_experts, self.correction, ctx.token_slot, idx, wts, self.top, self.n_groups,
-                       self.keep_groups, self.weight_scale, gate)
+                       self.keep_groups, self.weight_scale, gate, self.score, self.group_top)
         if h.dtype == torch.bfloat16 and self.w_gu_all.dtype == torch.bfloat16 \
                 and n * self.top >= DENSE_PAIRS_PER_EXPERT * self.n_experts:
             tail = self.shared_inner or 0
             act = ctx.rows("moe.act.dense", self.n_experts * self.inner + tail)
-            linear(h, self.w_gu_all, act, EPI_SWIGLU)
-            ops.moe_weigh_dense(act, self.n_experts, idx, wts, ctx.token_slot, tail, gate)
+            linear(h, self.w_gu_all, act, EPI_SWIGLU if self.gated else EPI_STORE)
+            ops.moe_weigh_dense(act, self.n_experts, idx, wts, ctx.token_slot, tail, gate, self.kind)
             linear(act, self.w_down_all, target, EPI_ACCUMULATE if accumulate else EPI_STORE)
             return
         ys = None
         if shared:
             act_s = ctx.rows("moe.shared.act", self.shared_inner)
-            linear(h, self.w_gu_all[self.routed_rows:], act_s, EPI_SWIGLU)
+            if self.gated:
+                linear(h, self.w_gu_all[self.routed_rows:], act_s, EPI_SWIGLU)
+            else:       # the up product with its activation: the chosen-experts kernel, for one expert all use
+                ops.moe_gate_up(h, self.w_gu_all[self.routed_rows:], 1, None, ctx.token_slot, act_s, self.kind)
             ys = ctx.rows("moe.shared.out", self.width, torch.float32)
             linear(act_s, self.ws_down, ys, EPI_STORE)
         act = ctx.rows("moe.act", self.top * self.inner).view(n * self.top, self.inner)
-        ops.moe_gate_up(h, self.w_gu, self.n_experts, idx, ctx.token_slot, act)
+        ops.moe_gate_up(h, self.w_gu, self.n_experts, idx, ctx.token_slot, act, self.kind)
         ops.moe_down(act, self.w_down, self.n_experts, idx, wts, ctx.token_slot, target, ys, gate, accumulate)

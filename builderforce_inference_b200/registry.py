@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its model.
 
 A config.json names its architecture under ``architectures[0]`` (a class name such as
-``Qwen3ForCausalLM``), ``model_type`` (``qwen3``) or ``architecture`` (``Datasun``, ``Bepilorn``).  Any of them selects the entry; the lookup is
+``Qwen3ForCausalLM``), ``model_type`` (``qwen3``) or ``architecture`` (``Datasun``, ``Bepilorn``, ``Munerax``).  Any of them selects the entry; the lookup is
 exact and case-sensitive, and an unknown name is answered with the list of known ones, as in
 the reference (crates/bfi-models/src/arch.rs:70-91).
 """
@@ -74,6 +74,10 @@ def _register_builtin() -> None:
     from .config.bepilorn import BepilornConfig
     register_architecture(("Bepilorn", "bepilorn"),
                           Architecture(name="bepilorn", config_class=BepilornConfig, describe=bepilorn.describe))
+    from .architectures import munerax
+    from .config.munerax import MuneraxConfig
+    register_architecture(("Munerax", "munerax"),
+                          Architecture(name="munerax", config_class=MuneraxConfig, describe=munerax.describe))
 
 
 _register_builtin()
