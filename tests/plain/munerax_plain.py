@@ -73,7 +73,7 @@ def bigram_rows(tokens, buckets, mul_prev, mul_cur):
 
 
 def embed(w, cfg, tokens):
-    e = cfg["embedding"]
+    e = cfg.get("embedding") or {}
     x = w["embed"][list(tokens)] * float(e.get("scale", 1.0))
     b = e.get("bigram")
     if b:
@@ -85,6 +85,8 @@ def embed(w, cfg, tokens):
 def rotate_half(x, positions, base, dims):
     """x [T, heads, d].  Of each head's first ``dims`` values, value i (i < dims/2) and value
     i + dims/2 form a pair that turns by the angle position * base^(-2i/dims); the rest pass."""
+    if not dims:
+        return x.clone()
     half = dims // 2
     i = torch.arange(half, dtype=F)
     freq = torch.tensor(float(base), dtype=F) ** (-2.0 * i / dims)
@@ -106,7 +108,8 @@ def latent_of(w, p, m, h, eps):
     d = h @ w[p + "dkv"].T
     c = norm(d[:, :r], w[p + "dkv.norm"], eps)
     kr = d[:, r:r + rd].reshape(T, 1, rd)
-    kr = rotate_half(kr, range(T), m["rot"]["base"], m["rot"]["dims"]).reshape(T, rd)
+    rot = m.get("rot") or {"base": 1.0, "dims": 0}
+    kr = rotate_half(kr, range(T), rot["base"], rot.get("dims", rd)).reshape(T, rd)
     return c, kr
 
 
@@ -128,7 +131,8 @@ def latent_attention(w, p, m, h, eps, latent):
     c, kr = latent
     q = (h @ w[p + "q"].T).reshape(T, H, d + rd)
     qn = q[..., :d]
-    qr = rotate_half(q[..., d:], range(T), m["rot"]["base"], m["rot"]["dims"])
+    rot = m.get("rot") or {"base": 1.0, "dims": 0}
+    qr = rotate_half(q[..., d:], range(T), rot["base"], rot.get("dims", rd))
     kn = (c @ w[p + "uk"].T).reshape(T, H, d)
     v = (c @ w[p + "uv"].T).reshape(T, H, dv)
     gate = torch.sigmoid(h @ w[p + "g"].T)                     # [T, H]
@@ -149,31 +153,39 @@ def expert(w, p, h):
     return relu_squared(h @ w[p + "up"].T) @ w[p + "down"].T
 
 
-def route(z, top, count, keep, scale):
+def route(z, top, count, keep, scale, margins=None):
     """Router logits z [T, E] -> (chosen experts [T, top], their weights [T, top]).  Scores are
     sigmoid(z); a group's score is the sum of its two largest; experts outside the ``keep`` best
-    groups cannot be chosen; the weights are the chosen scores times ``scale``."""
+    groups cannot be chosen; the weights are the chosen scores times ``scale``.  ``margins`` (a list)
+    receives, per token, by how much the last group kept and the last expert chosen won."""
     T, E = z.shape
     s = torch.sigmoid(z)
     allowed = torch.ones(T, E, dtype=torch.bool)
+    gap = torch.full((T,), math.inf, dtype=F)
     if count > 1 and keep < count:
         per = E // count
         g = s.reshape(T, count, per)
         gs = g.topk(min(2, per), dim=-1).values.sum(dim=-1)    # [T, count]
-        kept = gs.topk(keep, dim=-1).indices
+        order = gs.sort(dim=-1, descending=True)
+        gap = order.values[:, keep - 1] - order.values[:, keep]
         ok = torch.zeros(T, count, dtype=torch.bool)
-        ok.scatter_(1, kept, True)
+        ok.scatter_(1, order.indices[:, :keep], True)
         allowed = ok[:, :, None].expand(T, count, per).reshape(T, E)
-    pick = s.masked_fill(~allowed, -math.inf).topk(top, dim=-1).indices
+    order = s.masked_fill(~allowed, -math.inf).sort(dim=-1, descending=True)
+    if top < E:
+        gap = torch.minimum(gap, order.values[:, top - 1] - order.values[:, top])
+    if margins is not None:
+        margins.extend(float(v) for v in gap)
+    pick = order.indices[:, :top]
     return pick, s.gather(1, pick) * scale
 
 
-def routed_ff(w, p, f, h):
+def routed_ff(w, p, f, h, margins=None):
     r = f["router"]
     groups = r.get("groups") or {}
     count = groups.get("count", 1)
     z = h @ w[p + "router"].T
-    pick, weight = route(z, r["top"], count, groups.get("keep", count), float(r.get("scale", 1.0)))
+    pick, weight = route(z, r["top"], count, groups.get("keep", count), float(r.get("scale", 1.0)), margins)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=F)
     for t in range(h.shape[0]):
         for k in range(r["top"]):
@@ -185,8 +197,9 @@ def routed_ff(w, p, f, h):
 
 
 # ------------------------------------------------------------------------------- the model
-def forward_layers(w, cfg, tokens):
-    """The residual stream after every layer, [layers, T, width]."""
+def forward_layers(w, cfg, tokens, margins=None):
+    """The residual stream after every layer, [layers, T, width].  ``margins`` (a list) receives by
+    how much every routing decision was won."""
     eps = float(cfg["norm"]["eps"])
     x = embed(w, cfg, tokens)
     kept, after = {}, []
@@ -202,12 +215,12 @@ def forward_layers(w, cfg, tokens):
         f = layer.get("mlp")
         if f is not None:
             h = norm(x, w[p + "norm2"], eps)
-            x = x + (dense_ff(w, p + "mlp.", h) if f.get("kind", "dense") == "dense" else routed_ff(w, p + "mlp.", f, h))
+            x = x + (dense_ff(w, p + "mlp.", h) if f.get("kind", "dense") == "dense" else routed_ff(w, p + "mlp.", f, h, margins))
         after.append(x.clone())
     return torch.stack(after)
 
 
-def forward_each(w, cfg, tokens):
+def forward_each(w, cfg, tokens, margins=None):
     """Logits [T, vocab] at every position of ``tokens``."""
-    x = forward_layers(w, cfg, tokens)[-1]
+    x = forward_layers(w, cfg, tokens, margins)[-1]
     return norm(x, w["final.norm"], float(cfg["norm"]["eps"])) @ w["embed"].T
