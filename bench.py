@@ -356,6 +356,29 @@ def bepilorn_config(width, heads, kv, d, ff, layers):
                        for i in range(layers)]}
 
 
+MUNERAX_LATENT = 512           # values of the cached latent in the design runs; 64 more are the shared rotated key part
+
+
+def munerax_config(width, heads, kv, d, ff, layers):
+    """A Munerax model of these layer sizes: latent attention whose heads have half of the
+    attention's head size unrotated and half rotated, values of the attention's head size, and a
+    cache row of 512 + d/2 values; every fourth layer reads the cache of the layer before it; the
+    first layer's feed-forward is dense, the others' routed as Bepilorn's in these runs."""
+    half = d // 2
+    expert_ff = ff // 6 // 128 * 128
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "shared": {"ff": ff - 4 * expert_ff},
+           "router": {"experts": BEPILORN_EXPERTS, "top": 4, "scale": 1.0, "groups": {"count": 4, "keep": 2}}}
+    out = []
+    for i in range(layers):
+        mixer = {"heads": heads, "dim": half, "rot_dim": half, "vdim": d, "kv_rank": MUNERAX_LATENT, "scale": d ** -0.5,
+                 "rot": {"base": 1e6, "dims": half}}
+        if i % 4 == 3:
+            mixer["kv_from"] = i - 1
+        out.append({"type": "latent_attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff} if i == 0 else moe})
+    return {"architecture": "Munerax", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": out}
+
+
 def decode_breakdown(model, batch, ctx_len):
     """One instrumented single-token step (no graph, an event around every kernel) behind prompts of
     ``ctx_len`` tokens: milliseconds by kernel."""
@@ -389,14 +412,17 @@ def design_run(a) -> int:
         width, heads, kv, d, ff = DESIGN_SIZES[name]
         qwen3 = dict(CONFIG_4B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
                      num_key_value_heads=kv, head_dim=d, intermediate_size=ff, vocab_size=DESIGN_VOCAB)
-        if a.design == "bepilorn":      # beside the closest design the package has, and beside the dense one
+        if a.design == "munerax":       # beside the routed design and beside the dense softmax-attention one
+            configs = {"munerax": munerax_config(width, heads, kv, d, ff, layers),
+                       "bepilorn": bepilorn_config(width, heads, kv, d, ff, layers), "qwen3": qwen3}
+        elif a.design == "bepilorn":    # beside the closest design the package has, and beside the dense one
             configs = {"bepilorn": bepilorn_config(width, heads, kv, d, ff, layers),
                        "datasun": datasun_config(width, heads, kv, d, ff, layers), "qwen3": qwen3}
         else:
             configs = {"datasun": datasun_config(width, heads, kv, d, ff, layers), "qwen3": qwen3}
         for design, cfg in configs.items():
             model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=64 * 2048, max_seq_len=CONTEXT, max_batch=64)
-            by_kernel = a.design == "bepilorn"
+            by_kernel = a.design in ("bepilorn", "munerax")
             pf = prefill_run(model, PREFILL_TOKENS, 5, layers, breakdown=True, by_kernel=by_kernel)
             row = {"prefill_2048": {"ms": round(pf["ms"], 3), "tok_s": round(pf["tok_s"], 1), "breakdown": pf["breakdown"]}}
             for b in (8, 64):
@@ -411,8 +437,11 @@ def design_run(a) -> int:
             torch.cuda.empty_cache()
     pattern = {"datasun": "lightning x3, attention (window %d) x1" % DESIGN_WINDOW,
                "bepilorn": "state space x3, chunked attention (chunk %d) + gated linear attention x1; %d experts, 4 used, and a shared one"
-                           % (DESIGN_WINDOW, BEPILORN_EXPERTS)}[a.design]
-    print(json.dumps({"workloads": a.design + " beside " + ("datasun and qwen3" if a.design == "bepilorn" else "qwen3")
+                           % (DESIGN_WINDOW, BEPILORN_EXPERTS),
+               "munerax": "latent attention (cache row %d + head/2) x4, the fourth reading the third's cache; dense feed-forward in "
+                          "layer 0, then %d experts, 4 used, and a shared one" % (MUNERAX_LATENT, BEPILORN_EXPERTS)}[a.design]
+    beside = {"bepilorn": "datasun and qwen3", "munerax": "bepilorn and qwen3"}.get(a.design, "qwen3")
+    print(json.dumps({"workloads": a.design + " beside " + beside
                       + " at equal layer sizes, builder-run beside the benchmark", "dtype": "bf16",
                       "layers": layers, "pattern": pattern, "vocab": DESIGN_VOCAB,
                       "peaks": pk["source"], "sizes": out, "clocks": clocks.stop()}))
@@ -768,7 +797,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers of the same sizes")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--design", default=None, choices=["datasun", "bepilorn"],
+    ap.add_argument("--design", default=None, choices=["datasun", "bepilorn", "munerax"],
                     help="instead of the benchmark: this design beside qwen3 at equal layer sizes (see design_run)")
     ap.add_argument("--sizes", default=None, help="with --design: names of DESIGN_SIZES, comma-separated (default: all)")
     a = ap.parse_args()

@@ -76,8 +76,8 @@ def _latent(r: ConfigReader, index: int) -> MuneraxLatent:
     dim = r.integer("dim", minimum=1)
     rot_dim = r.integer("rot_dim", default=0, minimum=0)
     rank = r.integer("kv_rank", minimum=1)
-    if (rank + rot_dim) % 2 != 0 or rank + rot_dim > 512:
-        raise ConfigError(f"{r.what}: kv_rank + rot_dim = {rank + rot_dim} must be even and at most 512")
+    if (rank + rot_dim) % 2 != 0 or rank + rot_dim > 1024 or rank > 512:
+        raise ConfigError(f"{r.what}: kv_rank = {rank} must be at most 512, kv_rank + rot_dim = {rank + rot_dim} even and at most 1024")
     base, dims = None, 0
     rot = _sub(r, "rot", required=False)
     if rot is not None and rot_dim > 0:

@@ -24,8 +24,8 @@
 #define ATT_ROWS 16
 #define ATT_KEYS 32
 #define ATT_WARPS 8
-#define ATT_MAX_D 512
-#define ATT_MAX_NC (ATT_MAX_D / 32)
+#define ATT_MAX_D 1024        // keys
+#define ATT_MAX_DV 512        // values: 16 slices of 32 per lane
 
 template <typename T, int NC>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
@@ -240,7 +240,7 @@ extern "C" int bfi_attention_paged(const void* q, int dtype, long q_stride, void
                 n_q, n_kv);
     BFI_REQUIRE(d > 0 && d % 2 == 0 && d <= ATT_MAX_D, "attention_paged: head_dim %d must be even, at most %d",
                 d, ATT_MAX_D);
-    BFI_REQUIRE(dv > 0 && dv <= ATT_MAX_D, "attention_paged: value size %d must be positive, at most %d", dv, ATT_MAX_D);
+    BFI_REQUIRE(dv > 0 && dv <= ATT_MAX_DV, "attention_paged: value size %d must be positive, at most %d", dv, ATT_MAX_DV);
     BFI_REQUIRE(v_pages != nullptr || dv <= d, "attention_paged: values that are the keys' first %d values need keys that long", dv);
     BFI_REQUIRE(window >= 0 && chunk >= 0, "attention_paged: negative window or chunk");
     BFI_REQUIRE(has_sink != 2 || sinks != nullptr, "attention_paged: a sink per head needs its array");

@@ -27,7 +27,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "attention_paged.cu", "attention_prepare.cu", "lightning.cu",
              "recurrence.cu", "moe.cu", "latent.cu", "sublayer_out.cu", "sampling.cu", "utility.cu"],
     "fast": ["errors.cu", "skinny_gemm.cu", "attention_decode.cu", "attention_prefill.cu", "gemm_tcgen05.cu",
-             "attention_prefill_tcgen05.cu", "weight_stream.cu", "lightning_chunked.cu"],
+             "attention_prefill_tcgen05.cu", "attention_latent.cu", "weight_stream.cu", "lightning_chunked.cu"],
 }
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]

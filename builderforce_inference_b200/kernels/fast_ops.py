@@ -244,6 +244,51 @@ def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_head
         _ptr(sinks), c_int(1 if exact_weights else 0), _stream())
 
 
+LATENT_TILES_PER_RANGE = 8      # a key range of the latent attention is at least this many tiles of 32 keys
+
+
+def latent_splits(n_seqs: int, rows: int, max_pages: int, n_sm: int) -> int:
+    """Into how many key ranges every sequence's latent attention is cut: one when the step's query
+    rows alone fill the GPU; otherwise enough blocks to fill it, none shorter than
+    ``LATENT_TILES_PER_RANGE`` tiles.  Depends only on sizes that are fixed when a step is captured."""
+    blocks = n_seqs * ((rows + 63) // 64)
+    if blocks >= n_sm:
+        return 1
+    fill = (n_sm + blocks - 1) // blocks
+    longest = max(1, (2 * max_pages) // LATENT_TILES_PER_RANGE)
+    return max(1, min(fill, longest, 64))
+
+
+def attention_latent_bf16(ctx, q: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float, sinks=None,
+                          splits=None) -> bool:
+    """Tensor-core attention over a cache of one row per token whose first ``value_dim`` values are
+    the token's value, for any step.  ``q``: [tokens, heads * head_dim]; ``out``: [tokens, heads *
+    value_dim]; ``sinks``: float32, one per head, or None; ``splits``: the number of key ranges, for
+    tests (default: ``latent_splits``)."""
+    d, dv = kv.head_dim, kv.value_dim
+    if not kv.values_in_keys or kv.n_kv_heads != 1 or kv.window or kv.chunk:
+        return False
+    if q.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16 or not kv.k.is_contiguous():
+        return False
+    if sinks is not None and (sinks.dtype != torch.float32 or not sinks.is_contiguous()):
+        return False
+    max_pages = kv.block_table.shape[1]
+    bucket = getattr(ctx, "pages_bucket", 0)
+    if bucket:
+        max_pages = min(max_pages, bucket)
+    n_splits = int(splits) if splits else latent_splits(ctx.n_seqs, ctx.max_seq_tokens * n_heads, max_pages,
+                                                        sm_count(q.device))
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = ctx.workspace.vector("latent.part_o", q.shape[0] * n_heads * n_splits * dv, torch.float32)
+        part_ml = ctx.workspace.vector("latent.part_ml", q.shape[0] * n_heads * n_splits * 2, torch.float32)
+    return library("fast").call_optional(
+        "bfi_attention_latent_bf16", _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k),
+        _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
+        c_int(ctx.n_seqs), c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(d), c_int(dv), c_float(scale), _ptr(sinks),
+        c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream())
+
+
 TCGEN05_ATTENTION_MIN_TOKENS = 128     # shorter steps: the mma.sync kernel with 64-token tiles
 
 

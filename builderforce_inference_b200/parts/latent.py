@@ -19,7 +19,9 @@ the number of heads; a layer without a down projection of its own (``own_kv`` fa
 rows another layer's run has written, with its own ``W_uk`` and ``W_uv``.
 
 Launches: one product for queries, gate logits and down projection together; ``latent_prepare``
-(rotations, the latent's norm, the cache write); ``latent_absorb``; the paged attention;
+(rotations, the latent's norm, the cache write); ``latent_absorb``; the attention (in bfloat16 the
+tensor-core kernel over stacked (token, head) rows, cut into key ranges when a step has few rows;
+otherwise the general paged kernel);
 ``latent_expand`` (``W_uv`` and the gate); the output product, which adds into the residual stream.
 """
 from __future__ import annotations
@@ -43,8 +45,9 @@ class LatentAttention(Mixer):
         if n_heads < 1 or dim < 1 or rot_dim < 0 or v_dim < 1 or kv_rank < 1:
             raise ValueError(f"latent attention: bad sizes heads={n_heads} dim={dim} rot_dim={rot_dim} v_dim={v_dim} "
                              f"kv_rank={kv_rank}")
-        if (kv_rank + rot_dim) % 2 != 0 or kv_rank + rot_dim > 512:
-            raise ValueError(f"latent attention: kv_rank + rot_dim = {kv_rank + rot_dim} must be even and at most 512")
+        if (kv_rank + rot_dim) % 2 != 0 or kv_rank + rot_dim > 1024 or kv_rank > 512:
+            raise ValueError(f"latent attention: kv_rank = {kv_rank} must be at most 512, kv_rank + rot_dim = "
+                             f"{kv_rank + rot_dim} even and at most 1024")
         if not (sink is None or sink == "learned" or isinstance(sink, (int, float))):
             raise ValueError(f"sink must be a number or 'learned', got {sink!r}")
         self.width, self.n_heads, self.dim, self.rot_dim = int(width), int(n_heads), int(dim), int(rot_dim)
@@ -107,6 +110,8 @@ class LatentAttention(Mixer):
         self.w_o = tensors["o_proj"]
         self.dkv_norm = tensors["dkv_norm"].contiguous() if self.own_kv else None
         self.sinks = tensors["sink"].float().contiguous() if self.learned_sink else None
+        if self.sink is not None:          # one number for all heads: the tensor-core kernel reads one per head
+            self.sinks = torch.full((self.n_heads,), self.sink, dtype=torch.float32, device=self.w_uk.device)
 
     def forward(self, ctx, h, residual, run) -> None:
         self._run(ctx, h, residual, run, EPI_ACCUMULATE)
@@ -136,6 +141,10 @@ class LatentAttention(Mixer):
         linear(out, self.w_o, target, epilogue)
 
     def attend(self, ctx, qa, lat, kv) -> None:
+        if qa.dtype == torch.bfloat16:
+            from ..kernels import fast_ops
+            if fast_ops.attention_latent_bf16(ctx, qa, lat, kv, self.n_heads, self.scale, self.sinks):
+                return
         sink = self.sinks if self.learned_sink else self.sink
         ops.attention_paged(qa, qa.stride(0), lat, kv, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
                             ctx.n_seqs, ctx.max_seq_tokens, self.n_heads, self.scale, sink)

@@ -146,8 +146,9 @@ class Latent:
     """One latent attention layer given by its sizes: random matrices, and projection rows laid out
     as the kernels read them ([queries | gate logits | pad | down projection])."""
 
-    def __init__(self, heads, d, rd, dv, rank, rot, dt, seed=0, scale=0.2, base=100.0, eps=1e-5, pad=3):
+    def __init__(self, heads, d, rd, dv, rank, rot, dt, seed=0, scale=0.2, base=100.0, eps=1e-5, pad=3, splits=None):
         self.a, self.d, self.rd, self.dv, self.r, self.rot, self.dt = heads, d, rd, dv, rank, rot, dt
+        self.splits = splits          # not None: the tensor-core attention, cut into this many key ranges (0: its own choice)
         self.scale, self.base, self.eps = scale, base, eps
         g = torch.Generator().manual_seed(seed)
         self.g = g
@@ -199,8 +200,18 @@ class Latent:
                          cache.view, write)
         o.latent_absorb(p, self.uk.to(DEV), qa, i32(slot), a, d, rd, r)
         lat = torch.full((n, a * r), float("nan"), dtype=dt, device=DEV)
-        o.attention_paged(qa, qa.stride(0), lat, cache.view, i32(cu), i32([s for s, _, _ in seqs]), i32([st for _, st, _ in seqs]),
-                          len(seqs), max(t for _, _, t in seqs), a, self.scale, self.sink.float().to(DEV) if sink else None)
+        sinks = self.sink.float().to(DEV) if sink else None
+        if self.splits is not None:
+            from types import SimpleNamespace
+            from builderforce_inference_b200.engine.context import Workspace
+            from builderforce_inference_b200.kernels import fast_ops
+            ctx = SimpleNamespace(n_seqs=len(seqs), max_seq_tokens=max(t for _, _, t in seqs), cu_seqlens=i32(cu),
+                                  seq_slot=i32([s for s, _, _ in seqs]), seq_start=i32([st for _, st, _ in seqs]),
+                                  workspace=Workspace(DEV), pages_bucket=0)
+            assert fast_ops.attention_latent_bf16(ctx, qa, lat, cache.view, a, self.scale, sinks, splits=self.splits or None)
+        else:
+            o.attention_paged(qa, qa.stride(0), lat, cache.view, i32(cu), i32([s for s, _, _ in seqs]),
+                              i32([st for _, st, _ in seqs]), len(seqs), max(t for _, _, t in seqs), a, self.scale, sinks)
         out = torch.full((n, a * dv), 9.0, dtype=dt, device=DEV)
         o.latent_expand(lat, self.uv.to(DEV), p[:, self.gate_off:self.gate_off + a] if gate else None, out, i32(slot), a, dv, r)
         assert float((out[-1].float() - 9.0).abs().max()) == 0.0       # the padding row is left alone
@@ -246,14 +257,50 @@ def test_latent_kernels_in_a_mixed_batch(dt, heads, d, rd, dv, rank, rot):
     assert rel_err(got, L.plain(p0)[0]) < t and rel_err(got, r0) > 10 * t
 
 
-@pytest.mark.parametrize("dt", [F32, BF16])
+TC_SIZES = [(5, 48, 32, 40, 64, 32), (8, 64, 32, 64, 128, 32), (6, 128, 64, 128, 448, 64), (16, 32, 16, 24, 512, 16),
+            (2, 16, 16, 16, 16, 16), (40, 8, 16, 8, 48, 8), (1, 24, 32, 12, 256, 32)]
+
+
+@pytest.mark.parametrize("splits", [0, 1, 3, 7])
+@pytest.mark.parametrize("heads,d,rd,dv,rank,rot", TC_SIZES)
+def test_tensor_core_latent_attention_in_a_mixed_batch(heads, d, rd, dv, rank, rot, splits):
+    """The bfloat16 kernel over stacked (token, head) rows, whole and cut into key ranges (more ranges
+    than a short sequence has tiles too): a prompt, a portion that starts inside a page behind a cached
+    prefix, single tokens at a tile's and a page's first and last place, over pages that start as NaN."""
+    L = Latent(heads, d, rd, dv, rank, rot, BF16, seed=heads * 100 + d, splits=splits)
+    n0, n1, n2, n3, n4 = 70, 200, 65, 33, 32
+    ps = [L.rows(n) for n in (n0, n1, n2, n3, n4)]
+    refs = [L.plain(p)[0] for p in ps]
+    cache = Rows(5, 256, rank + rd, rank, BF16, seed=d)
+    L.run(ps[1][:37], cache, [(1, 0, 37)])
+    for i, n in ((2, n2), (3, n3), (4, n4)):
+        L.run(ps[i][:n - 1], cache, [(i, 0, n - 1)])
+    got = L.run(torch.cat([ps[0], ps[1][37:]]), cache, [(0, 0, n0), (1, 37, n1 - 37)])
+    assert rel_err(got, torch.cat([refs[0], refs[1][37:]])) < 2.5e-2
+    got = L.run(torch.cat([ps[i][-1:] for i in (2, 3, 4)]), cache, [(2, n2 - 1, 1), (3, n3 - 1, 1), (4, n4 - 1, 1)])
+    assert rel_err(got, torch.cat([refs[i][-1:] for i in (2, 3, 4)])) < 2.5e-2
+    # the general kernel on the same rows: the two differ by rounding only
+    G = Latent(heads, d, rd, dv, rank, rot, BF16, seed=heads * 100 + d)
+    both = [(0, 0, n0)]
+    assert rel_err(L.run(ps[0], cache, both, write=False), G.run(ps[0], cache, both, write=False)) < 1.5e-2
+
+
+def test_tensor_core_latent_attention_declines_what_it_does_not_take():
+    """Sizes that are not multiples of 16 run the general kernel; nothing is launched for them."""
+    for heads, d, rd, dv, rank, rot in [(3, 10, 6, 12, 14, 6), (4, 16, 8, 16, 24, 8)]:
+        L = Latent(heads, d, rd, dv, rank, rot, BF16, splits=0)
+        with pytest.raises(AssertionError):
+            L.run(L.rows(5), Rows(1, 64, rank + rd, rank, BF16), [(0, 0, 5)])
+
+
+@pytest.mark.parametrize("dt,splits", [(F32, None), (BF16, None), (BF16, 0), (BF16, 4)])
 @pytest.mark.parametrize("through", ["latent", "shared part"])
-def test_one_loud_key_far_back_at_page_borders_and_the_first_tokens(dt, through):
+def test_one_loud_key_far_back_at_page_borders_and_the_first_tokens(dt, splits, through):
     """One key among hundreds stands out for every query (through the latent, or through the shared
     key part's values that do not turn): the tokens from it on hear it, in a prompt, in a portion
     that starts behind it, and token by token; the tokens before it do not."""
-    for loud in (3, 63, 64, 65, 127, 128):
-        L = Latent(3, 8, 8, 6, 16, 4, dt, seed=loud)
+    for loud in (3, 31, 32, 63, 64, 65, 127, 128):
+        L = Latent(3, 8, 8 if splits is None else 16, 6, 16, 4, dt, seed=loud, splits=splits)
         n = 330
         proj = L.rows(n, amp=0.05)
         a, d, rd, r, ko = L.a, L.d, L.rd, L.r, L.kv_off
