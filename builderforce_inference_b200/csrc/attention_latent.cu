@@ -7,9 +7,11 @@
 // (token, head) pairs of a sequence are stacked, head fastest, into query rows, and a block owns
 // 16 * RG consecutive ones.  Row r belongs to token r / heads and sees keys up to that token's
 // position.  p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i)) with an optional learned sink per head.
+// With `gate`, head h's output of token t is multiplied by sigmoid(gate[t, h]) while it is still
+// float32 (a scalar per row, so it commutes with whatever matrix the values meet afterwards).
 //
-// Per tile of 32 keys (half a page), with 8 warps:
-//   A  scores: warp (row group, key group) multiplies its 16 rows by its 32 / (8 / RG) keys over all
+// Per tile of keys (half a page with 64 rows per block, a page with 32), with 8 warps:
+//   A  scores: warp (row group, key group) multiplies its 16 rows by its share of the keys over all
 //      of `d` (mma.sync.m16n8k16, float32 accumulators) and leaves them in shared memory as float32;
 //   B  softmax: 256 / rows threads per row: scale, mask, running maximum and sum in float32
 //      (ex2.approx on scores pre-multiplied by log2 e); the weights go back to shared memory as TWO
@@ -26,25 +28,31 @@
 
 #define AL_WARPS 8
 #define AL_THREADS (AL_WARPS * 32)
-#define AL_KEYS 32
-#define AL_PS 40                  // row stride of the weights' tiles, in bfloat16 (80 bytes: odd in 16-byte chunks)
-#define AL_SS 33                  // row stride of the score tile, in float32
+#define AL_PS(KT) ((KT) + 8)      // row stride of the weights' tiles, in bfloat16 (odd in 16-byte chunks)
+#define AL_SS(KT) ((KT) + 1)      // row stride of the score tile, in float32
 #define AL_LOG2E 1.4426950408889634f
 
-template <int RG, int NT>
+__device__ __forceinline__ float al_gate(const bf16* gate, long gate_stride, long token, int h) {
+    if (gate == nullptr) return 1.0f;
+    const float x = __bfloat162float(gate[(size_t)token * gate_stride + h]);
+    return 1.0f / (1.0f + expf(-x));          // expf(+large) = inf gives 0, expf(-large) = 0 gives 1
+}
+
+template <int RG, int NT, int AL_KEYS>
 __global__ void __launch_bounds__(AL_THREADS, 1)
 attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
                         const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                         const int* __restrict__ seq_start, int heads, int d, int dv, float scale_log2,
-                        const float* __restrict__ sinks, int n_splits, float* __restrict__ part_o,
-                        float* __restrict__ part_ml) {
+                        const float* __restrict__ sinks, const bf16* __restrict__ gate, long gate_stride, int n_splits,
+                        float* __restrict__ part_o, float* __restrict__ part_ml) {
     constexpr int QR = 16 * RG;               // query rows of a block
     constexpr int KG = AL_WARPS / RG;         // key groups in step A
     constexpr int KW = AL_KEYS / KG;          // keys of a warp in step A
     constexpr int KN = KW / 8;                // its score tiles of 8 keys
     constexpr int TPR = AL_THREADS / QR;      // threads per row in step B
     constexpr int KPT = AL_KEYS / TPR;        // keys per thread in step B
+    constexpr int PS = AL_PS(AL_KEYS), SS = AL_SS(AL_KEYS);
     pdl_trigger();
     pdl_wait();
     const int seq = blockIdx.z;
@@ -53,7 +61,8 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     const int t0 = cu_seqlens[seq];
     const int nt = cu_seqlens[seq + 1] - t0;
     const long n_rows = (long)nt * heads;
-    const long row0 = (long)blockIdx.x * QR;
+    // the last rows of a sequence walk the most keys: they start first
+    const long row0 = (long)(gridDim.x - 1 - blockIdx.x) * QR;
     if (row0 >= n_rows) return;
     const int start = seq_start[seq];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -62,11 +71,11 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* qs = reinterpret_cast<bf16*>(smem_raw);                     // [QR][dp]
-    bf16* ks[2] = {qs + QR * dp, qs + QR * dp + AL_KEYS * dp};        // [32][dp] each
-    bf16* ph = ks[1] + AL_KEYS * dp;                                  // [QR][AL_PS] rounded weights
-    bf16* pl = ph + QR * AL_PS;                                       // [QR][AL_PS] what the rounding left over
-    float* ss = reinterpret_cast<float*>(pl + QR * AL_PS);            // [QR][AL_SS] scores
-    float* corr_s = ss + QR * AL_SS;                                  // [QR] factor for the running output
+    bf16* ks[2] = {qs + QR * dp, qs + QR * dp + AL_KEYS * dp};        // [keys of a tile][dp] each
+    bf16* ph = ks[1] + AL_KEYS * dp;                                  // [QR][PS] rounded weights
+    bf16* pl = ph + QR * PS;                                       // [QR][PS] what the rounding left over
+    float* ss = reinterpret_cast<float*>(pl + QR * PS);            // [QR][SS] scores
+    float* corr_s = ss + QR * SS;                                  // [QR] factor for the running output
     float* m_s = corr_s + QR;                                         // [QR] final maximum
     float* l_s = m_s + QR;                                            // [QR] final sum
     __shared__ int tile_ok[2];
@@ -82,9 +91,10 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     const int chunks = d >> 3;
     const int* table = block_table + (size_t)slot * table_stride;
     auto issue = [&](int kt, int stage) {
-        const int page = table[kt >> 1];
+        constexpr int PER_PAGE = BFI_PAGE_TOKENS / AL_KEYS;           // tiles of a page
+        const int page = table[kt / PER_PAGE];
         if (threadIdx.x == 0) tile_ok[stage] = page >= 0;
-        const bf16* src = pages + ((size_t)(page < 0 ? 0 : page) * BFI_PAGE_TOKENS + (size_t)(kt & 1) * AL_KEYS) * d;
+        const bf16* src = pages + ((size_t)(page < 0 ? 0 : page) * BFI_PAGE_TOKENS + (size_t)(kt % PER_PAGE) * AL_KEYS) * d;
         const int key0 = kt * AL_KEYS;
         for (int i = threadIdx.x; i < AL_KEYS * chunks; i += AL_THREADS) {
             const int row = i / chunks, c = i - row * chunks;
@@ -146,28 +156,44 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
             const bf16* qrow = qs + (rg * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * dp + (lane >> 4) * 8;
             const bf16* krow = ktile + (kg * KW + (lane & 7)) * dp;
             const int ksteps = d >> 4;
-            for (int kk = 0; kk < ksteps; kk += 2) {
-                uint32_t a0[4], a1[4];
+            // two steps of 16 values per turn; the fragments of the next turn are asked for before this
+            // turn's products, so the tensor cores do not wait for shared memory
+            uint32_t a0[2][4], a1[2][4], b[2][KN][4];
+            auto fetch = [&](int kk, int buf) {
                 const bool two = kk + 1 < ksteps;
-                ldmatrix_x4(a0, qrow + kk * 16);
-                if (two) ldmatrix_x4(a1, qrow + kk * 16 + 16);
+                ldmatrix_x4(a0[buf], qrow + kk * 16);
+                ldmatrix_x4(a1[buf], qrow + (two ? kk + 1 : kk) * 16);
                 // lanes 16..31 address the second step's chunks; without one they repeat the first's
                 const int kc = 2 * kk + (two ? (lane >> 3) : ((lane >> 3) & 1));
 #pragma unroll
+                for (int j = 0; j < KN; ++j) ldmatrix_x4(b[buf][j], krow + j * 8 * dp + kc * 8);
+            };
+            fetch(0, 0);
+            int buf = 0;
+            for (int kk = 0; kk < ksteps; kk += 2, buf ^= 1) {
+                if (kk + 2 < ksteps) {
+                    if (buf == 0) fetch(kk + 2, 1);
+                    else fetch(kk + 2, 0);
+                }
+                const bool two = kk + 1 < ksteps;
+#pragma unroll
                 for (int j = 0; j < KN; ++j) {
-                    uint32_t b[4];
-                    ldmatrix_x4(b, krow + j * 8 * dp + kc * 8);
-                    mma16816(s[j], a0, b[0], b[1]);
-                    if (two) mma16816(s[j], a1, b[2], b[3]);
+                    if (buf == 0) {
+                        mma16816(s[j], a0[0], b[0][j][0], b[0][j][1]);
+                        if (two) mma16816(s[j], a1[0], b[0][j][2], b[0][j][3]);
+                    } else {
+                        mma16816(s[j], a0[1], b[1][j][0], b[1][j][1]);
+                        if (two) mma16816(s[j], a1[1], b[1][j][2], b[1][j][3]);
+                    }
                 }
             }
 #pragma unroll
             for (int j = 0; j < KN; ++j) {
-                float* dst = ss + (rg * 16 + g) * AL_SS + kg * KW + j * 8 + 2 * t;
+                float* dst = ss + (rg * 16 + g) * SS + kg * KW + j * 8 + 2 * t;
                 dst[0] = s[j][0];
                 dst[1] = s[j][1];
-                dst[8 * AL_SS] = s[j][2];
-                dst[8 * AL_SS + 1] = s[j][3];
+                dst[8 * SS] = s[j][2];
+                dst[8 * SS + 1] = s[j][3];
             }
         }
         __syncthreads();
@@ -180,7 +206,7 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 #pragma unroll
             for (int i = 0; i < KPT; ++i) {
                 const int key = kt * AL_KEYS + bsub * KPT + i;
-                float x = ss[brow * AL_SS + bsub * KPT + i] * scale_log2;
+                float x = ss[brow * SS + bsub * KPT + i] * scale_log2;
                 if (!ok || key > bpos) x = -INFINITY;
                 v[i] = x;
                 mx = fmaxf(mx, x);
@@ -203,8 +229,8 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
             for (int w = 1; w < TPR; w <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
             l_run = l_run * corr + sum;
             m_run = m_new;
-            uint32_t* dh = reinterpret_cast<uint32_t*>(ph + brow * AL_PS + bsub * KPT);
-            uint32_t* dl = reinterpret_cast<uint32_t*>(pl + brow * AL_PS + bsub * KPT);
+            uint32_t* dh = reinterpret_cast<uint32_t*>(ph + brow * PS + bsub * KPT);
+            uint32_t* dl = reinterpret_cast<uint32_t*>(pl + brow * PS + bsub * KPT);
 #pragma unroll
             for (int i = 0; i < KPT / 2; ++i) {
                 dh[i] = hi[i];
@@ -232,7 +258,7 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                 uint32_t ah[RG][4], al[RG][4];
 #pragma unroll
                 for (int a = 0; a < RG; ++a) {
-                    const int off = (a * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * AL_PS + k16 * 16 + (lane >> 4) * 8;
+                    const int off = (a * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * PS + k16 * 16 + (lane >> 4) * 8;
                     ldmatrix_x4(ah[a], ph + off);
                     ldmatrix_x4(al[a], pl + off);
                 }
@@ -288,7 +314,7 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
             } else {
                 float l_all = l;
                 if (sinks != nullptr && m > -INFINITY) l_all += fast_exp2(sinks[h] * AL_LOG2E - m);
-                const float inv = l_all > 0.0f ? 1.0f / l_all : 0.0f;
+                const float inv = l_all > 0.0f ? al_gate(gate, gate_stride, t0 + tok, h) / l_all : 0.0f;
                 bf16* orow = out + (size_t)(t0 + tok) * out_stride + (size_t)h * dv;
 #pragma unroll
                 for (int n = 0; n < NT; ++n) {
@@ -306,7 +332,8 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 __global__ void __launch_bounds__(128)
 attention_latent_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, bf16* __restrict__ out,
                               long out_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
-                              int heads, int dv, int n_splits, const float* __restrict__ sinks) {
+                              int heads, int dv, int n_splits, const float* __restrict__ sinks,
+                              const bf16* __restrict__ gate, long gate_stride) {
     pdl_trigger();
     pdl_wait();
     const int seq = blockIdx.z;
@@ -326,7 +353,7 @@ attention_latent_merge_kernel(const float* __restrict__ part_o, const float* __r
         if (mz > -INFINITY) l += part_ml[(pr + z) * 2 + 1] * fast_exp2(mz - m);
     }
     if (sinks != nullptr && m > -INFINITY) l += fast_exp2(sinks[h] * AL_LOG2E - m);
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    const float inv = l > 0.0f ? al_gate(gate, gate_stride, t0 + tok, h) / l : 0.0f;
     bf16* orow = out + (size_t)(t0 + tok) * out_stride + (size_t)h * dv;
     for (int c = threadIdx.x; c < dv; c += blockDim.x) {
         float acc = 0.0f;
@@ -338,15 +365,19 @@ attention_latent_merge_kernel(const float* __restrict__ part_o, const float* __r
     }
 }
 
-template <int RG, int NT>
+static size_t latent_smem(int rows, int keys, int d) {
+    return (size_t)(rows + 2 * keys) * (d + 8) * sizeof(bf16) + (size_t)2 * rows * AL_PS(keys) * sizeof(bf16) +
+           (size_t)rows * AL_SS(keys) * sizeof(float) + (size_t)3 * rows * sizeof(float);
+}
+
+template <int RG, int NT, int KT>
 static int launch_latent(const void* q, long q_stride, void* out, long out_stride, const void* pages, const int* block_table,
                          int table_stride, const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs,
-                         int max_tokens, int heads, int d, int dv, float scale, const float* sinks, int n_splits,
-                         float* part_o, float* part_ml, cudaStream_t stream) {
+                         int max_tokens, int heads, int d, int dv, float scale, const float* sinks, const bf16* gate,
+                         long gate_stride, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
     constexpr int QR = 16 * RG;
-    const size_t smem = (size_t)(QR + 2 * AL_KEYS) * (d + 8) * sizeof(bf16) + (size_t)2 * QR * AL_PS * sizeof(bf16) +
-                        (size_t)QR * AL_SS * sizeof(float) + (size_t)3 * QR * sizeof(float);
-    auto kernel = attention_latent_kernel<RG, NT>;
+    const size_t smem = latent_smem(QR, KT, d);
+    auto kernel = attention_latent_kernel<RG, NT, KT>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return bfi_fail("attention_latent: cannot reserve %zu bytes of shared memory: %s", smem,
@@ -355,12 +386,12 @@ static int launch_latent(const void* q, long q_stride, void* out, long out_strid
     const long rows = (long)max_tokens * heads;
     dim3 grid((unsigned)((rows + QR - 1) / QR), n_splits, n_seqs);
     bfi_launch(kernel, grid, dim3(AL_THREADS), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)pages,
-               block_table, table_stride, cu_seqlens, seq_slot, seq_start, heads, d, dv, scale * AL_LOG2E, sinks, n_splits, part_o,
-               part_ml);
+               block_table, table_stride, cu_seqlens, seq_slot, seq_start, heads, d, dv, scale * AL_LOG2E, sinks, gate, gate_stride,
+               n_splits, part_o, part_ml);
     if (bfi_check_launch("attention_latent")) return 1;
     if (n_splits > 1) {
         bfi_launch(attention_latent_merge_kernel, dim3((unsigned)rows, 1, n_seqs), dim3(128), 0, stream, (const float*)part_o,
-                   (const float*)part_ml, (bf16*)out, out_stride, cu_seqlens, seq_slot, heads, dv, n_splits, sinks);
+                   (const float*)part_ml, (bf16*)out, out_stride, cu_seqlens, seq_slot, heads, dv, n_splits, sinks, gate, gate_stride);
         return bfi_check_launch("attention_latent_merge");
     }
     return 0;
@@ -368,13 +399,15 @@ static int launch_latent(const void* q, long q_stride, void* out, long out_strid
 
 // Returns 0 on success, 1 on error, 2 when the shape is not taken (nothing launched).
 // `q` rows are [heads][d] per token, `out` rows [heads][dv]; `pages` is the cache ([pages][64 tokens][d]);
-// `sinks`: float32, one per head, or null.  `n_splits` > 1 needs `part_o` (tokens * heads * n_splits * dv
+// `sinks`: float32, one per head, or null.  `gate`: bfloat16 logits, [tokens][heads] with `gate_stride`
+// values between tokens, or null.  `n_splits` > 1 needs `part_o` (tokens * heads * n_splits * dv
 // floats) and `part_ml` (tokens * heads * n_splits * 2 floats).
 extern "C" int bfi_attention_latent_bf16(const void* q, long q_stride, void* out, long out_stride, const void* pages,
                                          const int* block_table, int table_stride, const int* cu_seqlens,
                                          const int* seq_slot, const int* seq_start, int n_seqs, int max_tokens, int heads,
-                                         int d, int dv, float scale, const float* sinks, int n_splits, float* part_o,
-                                         float* part_ml, cudaStream_t stream) {
+                                         int d, int dv, float scale, const float* sinks, const void* gate,
+                                         long gate_stride, int n_splits, float* part_o, float* part_ml,
+                                         cudaStream_t stream) {
     BFI_REQUIRE(heads > 0 && d > 0 && dv > 0 && dv <= d, "attention_latent: bad sizes heads=%d d=%d dv=%d", heads, d, dv);
     BFI_REQUIRE(n_splits >= 1 && (n_splits == 1 || (part_o != nullptr && part_ml != nullptr)),
                 "attention_latent: %d key ranges need their scratch", n_splits);
@@ -383,10 +416,13 @@ extern "C" int bfi_attention_latent_bf16(const void* q, long q_stride, void* out
     if (q_stride % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)out & 3) || ((uintptr_t)pages & 15) ||
         n_seqs > 65535 || n_splits > 65535)
         return 2;
-    const bool few = (long)max_tokens * heads <= 32;
+    if (latent_smem(64, 32, d) > 227 * 1024) return 2;
+    // few rows: blocks of 32 rows that take a whole page of keys per turn, where that fits
+    const bool few = (long)max_tokens * heads <= 32 && latent_smem(32, 64, d) <= 227 * 1024;
 #define BFI_AL_CASE(RG, NT)                                                                                               \
-    return launch_latent<RG, NT>(q, q_stride, out, out_stride, pages, block_table, table_stride, cu_seqlens, seq_slot,    \
-                                 seq_start, n_seqs, max_tokens, heads, d, dv, scale, sinks, n_splits, part_o, part_ml, stream)
+    return launch_latent<RG, NT, (RG == 2 ? 64 : 32)>(q, q_stride, out, out_stride, pages, block_table, table_stride, cu_seqlens, seq_slot,    \
+                                 seq_start, n_seqs, max_tokens, heads, d, dv, scale, sinks, (const bf16*)gate, gate_stride, n_splits, part_o,   \
+                                 part_ml, stream)
     if (few) {
         if (dv <= 128) BFI_AL_CASE(2, 2);
         if (dv <= 256) BFI_AL_CASE(2, 4);

@@ -123,14 +123,16 @@ extern "C" int bfi_latent_prepare(const void* proj, int dtype, long proj_stride,
 
 // ------------------------------------------------------------------------------------------
 // qa[t, h, j] = sum_e W_uk[h * d + e, j] * q[t, h, e]       j < rank
-// grid (token tiles, heads); a block stages LAT_TOK tokens' unrotated query values of its head as
-// float32 and walks W_uk_h once for all of them: thread j owns column j (and j + blockDim, ...), so
-// a row of W_uk_h is read by consecutive threads.
+// grid (token tiles, heads, column groups); a block stages LAT_TOK tokens' unrotated query values of
+// its head as float32 and walks its LAT_COLS columns of W_uk_h once for all of them: a thread owns
+// one column, so a row of W_uk_h is read by consecutive threads.  Few tokens still make heads *
+// rank / LAT_COLS blocks.
 // ------------------------------------------------------------------------------------------
 #define LAT_TOK 8
+#define LAT_COLS 64
 
 template <typename T, typename TW>
-__global__ void __launch_bounds__(LAT_THREADS)
+__global__ void __launch_bounds__(LAT_COLS)
 latent_absorb_kernel(const T* __restrict__ proj, long proj_stride, const TW* __restrict__ w_uk, T* __restrict__ qa,
                      long qa_stride, const int* __restrict__ token_slot, int n_tokens, int d, int rd, int rank) {
     pdl_trigger();
@@ -138,14 +140,15 @@ latent_absorb_kernel(const T* __restrict__ proj, long proj_stride, const TW* __r
     const int h = blockIdx.y;
     const int t0 = blockIdx.x * LAT_TOK;
     pdl_wait();
-    for (int i = threadIdx.x; i < LAT_TOK * d; i += LAT_THREADS) {
+    for (int i = threadIdx.x; i < LAT_TOK * d; i += LAT_COLS) {
         const int tt = i / d, e = i - tt * d;
         const int t = t0 + tt;
         qs[i] = (t < n_tokens && token_slot[t] >= 0) ? to_f32(proj[(size_t)t * proj_stride + (size_t)h * (d + rd) + e]) : 0.0f;
     }
     __syncthreads();
     const TW* w = w_uk + (size_t)h * d * rank;
-    for (int j = threadIdx.x; j < rank; j += LAT_THREADS) {
+    const int j = blockIdx.z * LAT_COLS + threadIdx.x;
+    if (j < rank) {
         float acc[LAT_TOK];
 #pragma unroll
         for (int tt = 0; tt < LAT_TOK; ++tt) acc[tt] = 0.0f;
@@ -170,24 +173,26 @@ extern "C" int bfi_latent_absorb(const void* proj, int dtype, long proj_stride, 
     BFI_REQUIRE(dtype == w_dtype || w_dtype == BFI_F32, "latent_absorb: weights of the activations' type or float32");
     BFI_REQUIRE((size_t)LAT_TOK * d * 4 <= 48 * 1024, "latent_absorb: %d unrotated values per head are too many", d);
     if (n_tokens <= 0) return 0;
-    const dim3 grid((n_tokens + LAT_TOK - 1) / LAT_TOK, n_heads);
+    const dim3 grid((n_tokens + LAT_TOK - 1) / LAT_TOK, n_heads, (rank + LAT_COLS - 1) / LAT_COLS);
+    BFI_REQUIRE(grid.z <= 65535, "latent_absorb: a latent of %d values is too large", rank);
     const size_t smem = (size_t)LAT_TOK * d * sizeof(float);
     if (dtype == BFI_F32)
-        bfi_launch(latent_absorb_kernel<float, float>, grid, dim3(LAT_THREADS), smem, stream, (const float*)proj, proj_stride,
+        bfi_launch(latent_absorb_kernel<float, float>, grid, dim3(LAT_COLS), smem, stream, (const float*)proj, proj_stride,
                    (const float*)w_uk, (float*)qa, qa_stride, token_slot, n_tokens, d, rd, rank);
     else if (w_dtype == BFI_F32)
-        bfi_launch(latent_absorb_kernel<bf16, float>, grid, dim3(LAT_THREADS), smem, stream, (const bf16*)proj, proj_stride,
+        bfi_launch(latent_absorb_kernel<bf16, float>, grid, dim3(LAT_COLS), smem, stream, (const bf16*)proj, proj_stride,
                    (const float*)w_uk, (bf16*)qa, qa_stride, token_slot, n_tokens, d, rd, rank);
     else
-        bfi_launch(latent_absorb_kernel<bf16, bf16>, grid, dim3(LAT_THREADS), smem, stream, (const bf16*)proj, proj_stride,
+        bfi_launch(latent_absorb_kernel<bf16, bf16>, grid, dim3(LAT_COLS), smem, stream, (const bf16*)proj, proj_stride,
                    (const bf16*)w_uk, (bf16*)qa, qa_stride, token_slot, n_tokens, d, rd, rank);
     return bfi_check_launch("latent_absorb");
 }
 
 // ------------------------------------------------------------------------------------------
 // o[t, h * dv + i] = (sum_j W_uv[h * dv + i, j] * lat[t, h * rank + j]) * sigmoid(gate[t, h])
-// grid (token tiles, heads); a block stages LAT_TOK tokens' latent outputs of its head as float32;
-// a warp owns an output row i of the head and walks W_uv's row once for all staged tokens.
+// grid (token tiles, heads, groups of 8 outputs); a block stages LAT_TOK tokens' latent outputs of
+// its head as float32; a warp owns ONE output row i of the head and walks W_uv's row once for all
+// staged tokens.  Few tokens still make heads * dv / 8 blocks.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ float lat_sigmoid(float x) {
     if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
@@ -219,7 +224,8 @@ latent_expand_kernel(const T* __restrict__ lat, long lat_stride, const TW* __res
     }
     __syncthreads();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int i = warp; i < dv; i += LAT_THREADS / 32) {
+    const int i = blockIdx.z * (LAT_THREADS / 32) + warp;
+    if (i < dv) {
         const TW* w = w_uv + ((size_t)h * dv + i) * rank;
         float acc[LAT_TOK];
 #pragma unroll
@@ -252,7 +258,8 @@ extern "C" int bfi_latent_expand(const void* lat, int dtype, long lat_stride, co
     const size_t smem = (size_t)(LAT_TOK * rank + LAT_TOK) * sizeof(float);
     BFI_REQUIRE(smem <= 48 * 1024, "latent_expand: a latent of %d values is too large", rank);
     if (n_tokens <= 0) return 0;
-    const dim3 grid((n_tokens + LAT_TOK - 1) / LAT_TOK, n_heads);
+    const dim3 grid((n_tokens + LAT_TOK - 1) / LAT_TOK, n_heads, (dv + LAT_THREADS / 32 - 1) / (LAT_THREADS / 32));
+    BFI_REQUIRE(grid.z <= 65535, "latent_expand: heads of %d values are too large", dv);
     if (dtype == BFI_F32)
         bfi_launch(latent_expand_kernel<float, float>, grid, dim3(LAT_THREADS), smem, stream, (const float*)lat, lat_stride,
                    (const float*)w_uv, (const float*)gate, gate_stride, (float*)out, out_stride, token_slot, n_tokens, dv, rank);

@@ -260,17 +260,20 @@ def latent_splits(n_seqs: int, rows: int, max_pages: int, n_sm: int) -> int:
 
 
 def attention_latent_bf16(ctx, q: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float, sinks=None,
-                          splits=None) -> bool:
+                          splits=None, gate=None) -> bool:
     """Tensor-core attention over a cache of one row per token whose first ``value_dim`` values are
     the token's value, for any step.  ``q``: [tokens, heads * head_dim]; ``out``: [tokens, heads *
-    value_dim]; ``sinks``: float32, one per head, or None; ``splits``: the number of key ranges, for
-    tests (default: ``latent_splits``)."""
+    value_dim]; ``sinks``: float32, one per head, or None; ``gate``: bfloat16 logits [tokens, heads]
+    (rows may be strided): head h's output of token t is multiplied by sigmoid(gate[t, h]); ``splits``:
+    the number of key ranges, for tests (default: ``latent_splits``)."""
     d, dv = kv.head_dim, kv.value_dim
     if not kv.values_in_keys or kv.n_kv_heads != 1 or kv.window or kv.chunk:
         return False
     if q.dtype != torch.bfloat16 or kv.k.dtype != torch.bfloat16 or not kv.k.is_contiguous():
         return False
     if sinks is not None and (sinks.dtype != torch.float32 or not sinks.is_contiguous()):
+        return False
+    if gate is not None and (gate.dtype != torch.bfloat16 or gate.stride(1) != 1 or gate.shape[1] != n_heads):
         return False
     max_pages = kv.block_table.shape[1]
     bucket = getattr(ctx, "pages_bucket", 0)
@@ -286,7 +289,7 @@ def attention_latent_bf16(ctx, q: torch.Tensor, out: torch.Tensor, kv, n_heads: 
         "bfi_attention_latent_bf16", _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(kv.k),
         _ptr(kv.block_table), c_int(kv.block_table.stride(0)), _ptr(ctx.cu_seqlens), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
         c_int(ctx.n_seqs), c_int(ctx.max_seq_tokens), c_int(n_heads), c_int(d), c_int(dv), c_float(scale), _ptr(sinks),
-        c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream())
+        _ptr(gate), c_long(gate.stride(0) if gate is not None else 0), c_int(n_splits), _ptr(part_o), _ptr(part_ml), _stream())
 
 
 TCGEN05_ATTENTION_MIN_TOKENS = 128     # shorter steps: the mma.sync kernel with 64-token tiles

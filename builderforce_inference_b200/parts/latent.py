@@ -21,8 +21,10 @@ rows another layer's run has written, with its own ``W_uk`` and ``W_uv``.
 Launches: one product for queries, gate logits and down projection together; ``latent_prepare``
 (rotations, the latent's norm, the cache write); ``latent_absorb``; the attention (in bfloat16 the
 tensor-core kernel over stacked (token, head) rows, cut into key ranges when a step has few rows;
-otherwise the general paged kernel);
+otherwise the general paged kernel, and the gate then waits for ``latent_expand``);
 ``latent_expand`` (``W_uv`` and the gate); the output product, which adds into the residual stream.
+In bfloat16 steps of more than ``PRODUCT_MIN_TOKENS`` tokens, ``latent_absorb`` and ``latent_expand``
+are one tensor-core product per head each, on slices of the same buffers.
 """
 from __future__ import annotations
 
@@ -38,6 +40,7 @@ from .base import MIXERS, POSITION_ENCODINGS, KVNeed, Mixer, ParamSpec, PartSpec
 @MIXERS.register("latent_attention")
 class LatentAttention(Mixer):
     graph_safe = True
+    PRODUCT_MIN_TOKENS = 64     # steps of more tokens: W_uk^T and W_uv as one matrix product per head
 
     def __init__(self, width: int, n_heads: int, dim: int, rot_dim: int, v_dim: int, kv_rank: int,
                  position: Optional[PartSpec] = None, eps: float = 1e-6, scale: Optional[float] = None,
@@ -107,6 +110,12 @@ class LatentAttention(Mixer):
         self.w_in = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
         self.w_uk = tensors["uk_proj"].contiguous()
         self.w_uv = tensors["uv_proj"].contiguous()
+        # steps of many tokens take W_uk^T and W_uv to the tensor cores head by head: W_uk_a^T as a
+        # matrix of its own ([kv_rank, dim]), when every slice starts on 16 bytes
+        sizes = (self.dim, self.dim + self.rot_dim, self.kv_rank, self.kv_rank + self.rot_dim, self.v_dim, self.w_in.shape[0])
+        self.w_uk_t = None
+        if self.w_uk.dtype == torch.bfloat16 and all(n % 8 == 0 for n in sizes):
+            self.w_uk_t = self.w_uk.view(self.n_heads, self.dim, self.kv_rank).transpose(1, 2).contiguous()
         self.w_o = tensors["o_proj"]
         self.dkv_norm = tensors["dkv_norm"].contiguous() if self.own_kv else None
         self.sinks = tensors["sink"].float().contiguous() if self.learned_sink else None
@@ -132,19 +141,34 @@ class LatentAttention(Mixer):
         qa = ctx.rows("latent.q", a * (r + rd))
         ops.latent_prepare(proj, qa, a, self.dim, rd, r, self.kv_off, self.dkv_norm, self.eps, table, rot_used,
                            ctx.token_pos, ctx.token_slot, kv, run.writes_cache, ctx.status)
-        ops.latent_absorb(proj, self.w_uk, qa, ctx.token_slot, a, self.dim, rd, r)
+        products = self.w_uk_t is not None and proj.dtype == torch.bfloat16 and ctx.n_tokens > self.PRODUCT_MIN_TOKENS
+        if products:
+            dq = self.dim + rd
+            for i in range(a):
+                linear(proj[:, i * dq:i * dq + self.dim], self.w_uk_t[i], qa[:, i * (r + rd):i * (r + rd) + r], EPI_STORE)
+        else:
+            ops.latent_absorb(proj, self.w_uk, qa, ctx.token_slot, a, self.dim, rd, r)
         lat = ctx.rows("latent.out", a * r)
-        self.attend(ctx, qa, lat, kv)
-        out = ctx.rows("attn.out", a * self.v_dim)
         gate = proj[:, self.gate_off:self.gate_off + a] if self.has_gate else None
-        ops.latent_expand(lat, self.w_uv, gate, out, ctx.token_slot, a, self.v_dim, r)
+        if self.attend(ctx, qa, lat, kv, gate):
+            gate = None                    # the attention has applied it
+        out = ctx.rows("attn.out", a * self.v_dim)
+        if products and gate is None:
+            dv = self.v_dim
+            for i in range(a):
+                linear(lat[:, i * r:(i + 1) * r], self.w_uv[i * dv:(i + 1) * dv], out[:, i * dv:(i + 1) * dv], EPI_STORE)
+        else:
+            ops.latent_expand(lat, self.w_uv, gate, out, ctx.token_slot, a, self.v_dim, r)
         linear(out, self.w_o, target, epilogue)
 
-    def attend(self, ctx, qa, lat, kv) -> None:
+    def attend(self, ctx, qa, lat, kv, gate=None) -> bool:
+        """The attention in the latent space; True if it has multiplied the heads' outputs by their
+        gates (a scalar per token and head, so it commutes with ``W_uv``)."""
         if qa.dtype == torch.bfloat16:
             from ..kernels import fast_ops
-            if fast_ops.attention_latent_bf16(ctx, qa, lat, kv, self.n_heads, self.scale, self.sinks):
-                return
+            if fast_ops.attention_latent_bf16(ctx, qa, lat, kv, self.n_heads, self.scale, self.sinks, gate=gate):
+                return gate is not None
         sink = self.sinks if self.learned_sink else self.sink
         ops.attention_paged(qa, qa.stride(0), lat, kv, ctx.cu_seqlens, ctx.seq_slot, ctx.seq_start,
                             ctx.n_seqs, ctx.max_seq_tokens, self.n_heads, self.scale, sink)
+        return False

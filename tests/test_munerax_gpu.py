@@ -208,7 +208,10 @@ class Latent:
             ctx = SimpleNamespace(n_seqs=len(seqs), max_seq_tokens=max(t for _, _, t in seqs), cu_seqlens=i32(cu),
                                   seq_slot=i32([s for s, _, _ in seqs]), seq_start=i32([st for _, st, _ in seqs]),
                                   workspace=Workspace(DEV), pages_bucket=0)
-            assert fast_ops.attention_latent_bf16(ctx, qa, lat, cache.view, a, self.scale, sinks, splits=self.splits or None)
+            # the kernel multiplies by the gates itself; the expansion then gets none
+            assert fast_ops.attention_latent_bf16(ctx, qa, lat, cache.view, a, self.scale, sinks, splits=self.splits or None,
+                                                  gate=p[:, self.gate_off:self.gate_off + a] if gate else None)
+            gate = False
         else:
             o.attention_paged(qa, qa.stride(0), lat, cache.view, i32(cu), i32([s for s, _, _ in seqs]),
                               i32([st for _, st, _ in seqs]), len(seqs), max(t for _, _, t in seqs), a, self.scale, sinks)
@@ -258,7 +261,7 @@ def test_latent_kernels_in_a_mixed_batch(dt, heads, d, rd, dv, rank, rot):
 
 
 TC_SIZES = [(5, 48, 32, 40, 64, 32), (8, 64, 32, 64, 128, 32), (6, 128, 64, 128, 448, 64), (16, 32, 16, 24, 512, 16),
-            (2, 16, 16, 16, 16, 16), (40, 8, 16, 8, 48, 8), (1, 24, 32, 12, 256, 32)]
+            (2, 16, 16, 16, 16, 16), (40, 8, 16, 8, 48, 8), (1, 24, 32, 12, 256, 32), (2, 8, 192, 8, 512, 64)]
 
 
 @pytest.mark.parametrize("splits", [0, 1, 3, 7])
