@@ -96,13 +96,15 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
         if (threadIdx.x == 0) tile_ok[stage] = page >= 0;
         const bf16* src = pages + ((size_t)(page < 0 ? 0 : page) * BFI_PAGE_TOKENS + (size_t)(kt % PER_PAGE) * AL_KEYS) * d;
         const int key0 = kt * AL_KEYS;
-        for (int i = threadIdx.x; i < AL_KEYS * chunks; i += AL_THREADS) {
-            const int row = i / chunks, c = i - row * chunks;
-            bf16* dst = ks[stage] + row * dp + c * 8;
+        for (int row = warp; row < AL_KEYS; row += AL_WARPS) {        // a warp per row, a lane per 16 bytes
             // rows that no query of the block sees may never have been written: zeros, so that a zero
             // weight times a stray NaN cannot reach the output
-            if (page >= 0 && key0 + row <= hi_block) cp_async16(dst, src + (size_t)row * d + c * 8);
-            else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+            const bool live = page >= 0 && key0 + row <= hi_block;
+            for (int c = lane; c < chunks; c += 32) {
+                bf16* dst = ks[stage] + row * dp + c * 8;
+                if (live) cp_async16(dst, src + (size_t)row * d + c * 8);
+                else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
+            }
         }
         cp_async_commit();
     };
@@ -148,11 +150,11 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 
         // ---- A: scores of 16 rows x KW keys
         {
-            float s[KN][4];
+            float s[KN][4], s2[KN][4];            // even and odd steps: two chains of products, not one
 #pragma unroll
             for (int j = 0; j < KN; ++j)
 #pragma unroll
-                for (int c = 0; c < 4; ++c) s[j][c] = 0.0f;
+                for (int c = 0; c < 4; ++c) s[j][c] = s2[j][c] = 0.0f;
             const bf16* qrow = qs + (rg * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * dp + (lane >> 4) * 8;
             const bf16* krow = ktile + (kg * KW + (lane & 7)) * dp;
             const int ksteps = d >> 4;
@@ -180,25 +182,26 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                 for (int j = 0; j < KN; ++j) {
                     if (buf == 0) {
                         mma16816(s[j], a0[0], b[0][j][0], b[0][j][1]);
-                        if (two) mma16816(s[j], a1[0], b[0][j][2], b[0][j][3]);
+                        if (two) mma16816(s2[j], a1[0], b[0][j][2], b[0][j][3]);
                     } else {
                         mma16816(s[j], a0[1], b[1][j][0], b[1][j][1]);
-                        if (two) mma16816(s[j], a1[1], b[1][j][2], b[1][j][3]);
+                        if (two) mma16816(s2[j], a1[1], b[1][j][2], b[1][j][3]);
                     }
                 }
             }
 #pragma unroll
             for (int j = 0; j < KN; ++j) {
                 float* dst = ss + (rg * 16 + g) * SS + kg * KW + j * 8 + 2 * t;
-                dst[0] = s[j][0];
-                dst[1] = s[j][1];
-                dst[8 * SS] = s[j][2];
-                dst[8 * SS + 1] = s[j][3];
+                dst[0] = s[j][0] + s2[j][0];
+                dst[1] = s[j][1] + s2[j][1];
+                dst[8 * SS] = s[j][2] + s2[j][2];
+                dst[8 * SS + 1] = s[j][3] + s2[j][3];
             }
         }
         __syncthreads();
 
         // ---- B: softmax of this thread's row over its KPT keys
+        bool moved;
         {
             const bool ok = tile_ok[stage] != 0;
             float v[KPT];
@@ -237,11 +240,13 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                 dl[i] = lo[i];
             }
             if (bsub == 0) corr_s[brow] = corr;
+            moved = corr != 1.0f && m_new != -INFINITY;      // a row that has seen no key has nothing to rescale
         }
-        __syncthreads();
+        const bool rescale = __syncthreads_or(moved);     // once the maxima have settled nothing is rescaled
 
         // ---- C: output += P V over this warp's columns, all rows
         if (col0 < dv) {
+            if (rescale)
 #pragma unroll
             for (int a = 0; a < RG; ++a) {
                 const float c0 = corr_s[a * 16 + g], c1 = corr_s[a * 16 + g + 8];
@@ -272,6 +277,9 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                     for (int a = 0; a < RG; ++a) {
                         mma16816(o[a][n], ah[a], b[0], b[1]);
                         mma16816(o[a][n + 1], ah[a], b[2], b[3]);
+                    }
+#pragma unroll
+                    for (int a = 0; a < RG; ++a) {
                         mma16816(o[a][n], al[a], b[0], b[1]);
                         mma16816(o[a][n + 1], al[a], b[2], b[3]);
                     }
