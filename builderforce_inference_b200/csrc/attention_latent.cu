@@ -5,7 +5,7 @@
 // `dv` values are also its value.  Every query head brings a row of `d` values (its unrotated part
 // already taken into the latent space), so all heads of all tokens read the same rows: the
 // (token, head) pairs of a sequence are stacked, head fastest, into query rows, and a block owns
-// 16 * RG consecutive ones.  Row r belongs to token r / heads and sees keys up to that token's
+// 16 * RG consecutive ones (RG = 1, 2 or 4).  Row r belongs to token r / heads and sees keys up to that token's
 // position.  p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i)) with an optional learned sink per head.
 // With `gate`, head h's output of token t is multiplied by sigmoid(gate[t, h]) while it is still
 // float32 (a scalar per row, so it commutes with whatever matrix the values meet afterwards).
@@ -425,12 +425,18 @@ extern "C" int bfi_attention_latent_bf16(const void* q, long q_stride, void* out
         n_seqs > 65535 || n_splits > 65535)
         return 2;
     if (latent_smem(64, 32, d) > 227 * 1024) return 2;
-    // few rows: blocks of 32 rows that take a whole page of keys per turn, where that fits
-    const bool few = (long)max_tokens * heads <= 32 && latent_smem(32, 64, d) <= 227 * 1024;
 #define BFI_AL_CASE(RG, NT)                                                                                               \
-    return launch_latent<RG, NT, (RG == 2 ? 64 : 32)>(q, q_stride, out, out_stride, pages, block_table, table_stride, cu_seqlens, seq_slot,    \
+    return launch_latent<RG, NT, (RG == 4 ? 32 : 64)>(q, q_stride, out, out_stride, pages, block_table, table_stride, cu_seqlens, seq_slot,    \
                                  seq_start, n_seqs, max_tokens, heads, d, dv, scale, sinks, (const bf16*)gate, gate_stride, n_splits, part_o,   \
                                  part_ml, stream)
+    // few rows: blocks of 16 or 32 rows that take a whole page of keys per turn, where that fits
+    const long rows = (long)max_tokens * heads;
+    const bool few = rows <= 32 && latent_smem(32, 64, d) <= 227 * 1024;
+    if (rows <= 16 && latent_smem(16, 64, d) <= 227 * 1024) {
+        if (dv <= 128) BFI_AL_CASE(1, 2);
+        if (dv <= 256) BFI_AL_CASE(1, 4);
+        BFI_AL_CASE(1, 8);
+    }
     if (few) {
         if (dv <= 128) BFI_AL_CASE(2, 2);
         if (dv <= 256) BFI_AL_CASE(2, 4);
