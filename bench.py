@@ -458,7 +458,8 @@ def kernel_run(a) -> int:
     ``--kernel attention_decode|attention_prefill|attention_prefill_tcgen05 --rows B_or_T --ctx C``
     (``--seqs N``: N prompts of --rows tokens each),
     ``--kernel qk_norm_rope --rows T``, ``--kernel decay_scan --rows T [--seqs N]`` / ``--kernel decay_step --rows B`` (the
-    recurrence with a step size per head over prompts / over single tokens), ``--kernel weight_stream --shape S [--stages R] [--ksplit Z]`` (the
+    recurrence with a step size per head over prompts / over single tokens), ``--kernel attention_latent --seqs N --rows T --ctx C
+    --heads H`` (the latent attention; --rows 1: single tokens behind C cached ones), ``--kernel weight_stream --shape S [--stages R] [--ksplit Z]`` (the
     matrix read once through the few-row products' TMA rings and nothing else: the floor under
     them).  Weights rotate over enough copies to exceed L2.  Prints one JSON line."""
     import torch
@@ -612,6 +613,38 @@ def kernel_run(a) -> int:
         bytes_moved = t * (2 * nq + 3 * nkv) * d * 2          # q read and written, k and v read and written to the cache
         flops = 0.0
         what = {"tokens": t, "q_heads": nq, "kv_heads": nkv, "head_dim": d}
+    elif a.kernel == "attention_latent":
+        # the latent attention over a cache of one row per token (512 + 64 values, the first 512 the value): --seqs
+        # sequences that bring --rows tokens each behind --ctx cached ones in all (--rows 1: single tokens)
+        from builderforce_inference_b200.cache import KVView
+        from builderforce_inference_b200.engine.context import Workspace
+        from types import SimpleNamespace
+        heads, rank, d = a.heads, MUNERAX_LATENT, MUNERAX_LATENT + 64
+        n_seq, t_new = a.seqs, a.rows
+        ctx_len = max(a.ctx, t_new)
+        blocks = (ctx_len + 63) // 64
+        n_pages = n_seq * blocks
+        table = torch.randperm(n_pages).to(torch.int32).reshape(n_seq, blocks).to(dev)
+        copies = max(2, int(400e6 // (n_pages * 64 * d * 2)) + 1) if t_new == 1 else 1
+        kvs = []
+        for _ in range(copies):
+            k = (torch.randn(n_pages, 1, 64, d, device=dev) * 0.5).to(torch.bfloat16)
+            kvs.append(KVView(k, k, table, 1, d, None, v_dim=rank, values_in_keys=True))
+        q = (torch.randn(n_seq * t_new, heads * d, device=dev) * 0.1).to(torch.bfloat16)
+        out = torch.empty(n_seq * t_new, heads * rank, device=dev, dtype=torch.bfloat16)
+        ctx = SimpleNamespace(n_seqs=n_seq, max_seq_tokens=t_new, workspace=Workspace(dev), pages_bucket=0,
+                              cu_seqlens=torch.arange(0, (n_seq + 1) * t_new, t_new, dtype=torch.int32, device=dev),
+                              seq_slot=torch.arange(n_seq, dtype=torch.int32, device=dev),
+                              seq_start=torch.full((n_seq,), ctx_len - t_new, dtype=torch.int32, device=dev))
+        sinks = torch.zeros(heads, device=dev)
+
+        def one(i):
+            if not fast_ops.attention_latent_bf16(ctx, q, out, kvs[i % copies], heads, d ** -0.5, sinks):
+                raise SystemExit("attention_latent does not take this shape")
+        pairs = n_seq * heads * sum(ctx_len - t_new + i + 1 for i in range(t_new))
+        bytes_moved = n_seq * ctx_len * d * 2 + n_seq * t_new * heads * (d + rank) * 2
+        flops = 2.0 * pairs * (d + rank)                # scores over the whole row, the weighted sum over the latent
+        what = {"seqs": n_seq, "new_tokens": t_new, "context": ctx_len, "heads": heads, "row": d, "latent": rank}
     else:
         from builderforce_inference_b200.cache import KVView
         c = CONFIG_4B
@@ -777,10 +810,11 @@ def main() -> int:
     ap.add_argument("--timeline", action="store_true", help="print one decode step's kernels on the GPU's clock (see timeline_run)")
     ap.add_argument("--timeline-layer", type=int, default=6)
     ap.add_argument("--timeline-prompt", type=int, default=0, help="with --timeline: a prompt step of this many tokens instead")
+    ap.add_argument("--heads", type=int, default=16, help="--kernel attention_latent: query heads")
     ap.add_argument("--seqs", type=int, default=1, help="kernel mode, prompt attention: prompts of --rows tokens each")
     ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "weight_stream", "qk_norm_rope", "attention_decode",
                                                        "attention_prefill", "attention_prefill_tcgen05", "lightning_chunks", "lightning_scan",
-                                                       "qk_prepare", "decay_scan", "decay_step"],
+                                                       "qk_prepare", "decay_scan", "decay_step", "attention_latent"],
                     help="time one kernel instead of the model (see kernel_run)")
     ap.add_argument("--shape", default="qkv", choices=sorted(KERNEL_SHAPES))
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of one CUDA graph")
