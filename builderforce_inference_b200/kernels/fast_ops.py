@@ -249,14 +249,21 @@ LATENT_TILES_PER_RANGE = 8      # a key range of the latent attention is at leas
 
 def latent_splits(n_seqs: int, rows: int, max_pages: int, n_sm: int) -> int:
     """Into how many key ranges every sequence's latent attention is cut: one when the step's query
-    rows alone fill the GPU; otherwise enough blocks to fill it, none shorter than
+    rows alone fill the GPU; otherwise the count whose blocks leave the fewest SMs idle.  With ``s``
+    ranges the launch has ``blocks * s`` blocks of ``1 / s`` of a sequence's keys each, one per SM at
+    a time, so it takes ``ceil(blocks * s / n_sm) / s`` of one block's whole walk; every further
+    range adds a partial output to write and merge, counted as 2% of that.  No range is shorter than
     ``LATENT_TILES_PER_RANGE`` tiles.  Depends only on sizes that are fixed when a step is captured."""
     blocks = n_seqs * ((rows + 63) // 64)
     if blocks >= n_sm:
         return 1
-    fill = (n_sm + blocks - 1) // blocks
-    longest = max(1, (2 * max_pages) // LATENT_TILES_PER_RANGE)
-    return max(1, min(fill, longest, 64))
+    longest = max(1, min((2 * max_pages) // LATENT_TILES_PER_RANGE, 64))
+    best, best_cost = 1, float(-(-blocks // n_sm))
+    for s in range(2, longest + 1):
+        cost = -(-blocks * s // n_sm) / s * (1.0 + 0.02 * s)
+        if cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
 
 
 def attention_latent_bf16(ctx, q: torch.Tensor, out: torch.Tensor, kv, n_heads: int, scale: float, sinks=None,
