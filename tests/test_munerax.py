@@ -243,3 +243,26 @@ def test_plain_model_is_causal_and_borrowers_read_their_source():
     # the previous token matters through the bigram table only
     other = P.forward_each(w, MX_ODD, [8] + ids[1:])
     assert not torch.allclose(other[1], full[1])
+
+
+def test_key_ranges_of_the_latent_attention_fill_whole_waves():
+    from builderforce_inference_b200.kernels.fast_ops import LATENT_TILES_PER_RANGE, latent_splits
+    n_sm = 148
+    for n_seqs in (1, 2, 7, 8, 31, 32, 64, 100, 147, 148, 400):
+        for rows in (1, 16, 32, 64, 65, 640):
+            for pages in (1, 3, 16, 64, 512):
+                s = latent_splits(n_seqs, rows, pages, n_sm)
+                blocks = n_seqs * ((rows + 63) // 64)
+                longest = max(1, min(2 * pages // LATENT_TILES_PER_RANGE, 64))
+                assert 1 <= s <= longest
+                if blocks >= n_sm:
+                    assert s == 1
+                    continue
+                # no other count within the bounds does the walk in fewer wave-lengths, the merge's share counted
+                def cost(k):
+                    return -(-blocks * k // n_sm) / k * (1.0 if k == 1 else 1.0 + 0.02 * k)
+                assert all(cost(s) <= cost(k) + 1e-9 for k in range(1, longest + 1)), (n_seqs, rows, pages, s)
+    # 64 sequences on 148 SMs: two ranges are one wave of half walks; three would be two waves of thirds
+    assert latent_splits(64, 16, 64, n_sm) == 2
+    # a single sequence is cut as far as its length allows
+    assert latent_splits(1, 16, 512, n_sm) == 64 and latent_splits(1, 16, 8, n_sm) == 2 and latent_splits(1, 16, 3, n_sm) == 1
