@@ -244,7 +244,7 @@ def attention_prefill_bf16(ctx, qkv: torch.Tensor, out: torch.Tensor, kv, n_head
         _ptr(sinks), c_int(1 if exact_weights else 0), _stream())
 
 
-LATENT_TILES_PER_RANGE = 8      # a key range of the latent attention is at least this many tiles of 32 keys
+LATENT_TILES_PER_RANGE = 4      # a key range of the latent attention is at least this many tiles of 32 keys
 
 
 def latent_splits(n_seqs: int, rows: int, max_pages: int, n_sm: int) -> int:

@@ -265,4 +265,5 @@ def test_key_ranges_of_the_latent_attention_fill_whole_waves():
     # 64 sequences on 148 SMs: two ranges are one wave of half walks; three would be two waves of thirds
     assert latent_splits(64, 16, 64, n_sm) == 2
     # a single sequence is cut as far as its length allows
-    assert latent_splits(1, 16, 512, n_sm) == 64 and latent_splits(1, 16, 8, n_sm) == 2 and latent_splits(1, 16, 3, n_sm) == 1
+    assert latent_splits(1, 16, 512, n_sm) == 64 and latent_splits(1, 16, 8, n_sm) == 16 // LATENT_TILES_PER_RANGE
+    assert latent_splits(1, 16, 1, n_sm) == 1
