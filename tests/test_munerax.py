@@ -249,7 +249,7 @@ def test_key_ranges_of_the_latent_attention_fill_whole_waves():
     from builderforce_inference_b200.kernels.fast_ops import LATENT_TILES_PER_RANGE, latent_splits
     n_sm = 148
     for n_seqs in (1, 2, 7, 8, 31, 32, 64, 100, 147, 148, 400):
-        for rows in (1, 16, 32, 64, 65, 640):
+        for rows in (1, 16, 32, 64, 65, 600):
             for pages in (1, 3, 16, 64, 512):
                 s = latent_splits(n_seqs, rows, pages, n_sm)
                 blocks = n_seqs * ((rows + 63) // 64)
