@@ -10,10 +10,13 @@
 // With `gate`, head h's output of token t is multiplied by sigmoid(gate[t, h]) while it is still
 // float32 (a scalar per row, so it commutes with whatever matrix the values meet afterwards).
 //
-// Per tile of keys (half a page with 64 rows per block, a page with 32), with 8 warps:
-//   A  scores: warp (row group, key group) multiplies its 16 rows by its share of the keys over all
-//      of `d` (mma.sync.m16n8k16, float32 accumulators) and leaves them in shared memory as float32;
-//   B  softmax: 256 / rows threads per row: scale, mask, running maximum and sum in float32
+// Per tile of keys (half a page with 64 rows per block, a page with 32 or 16), with NW warps (8; 16
+// when a block has 16 rows: such a block is bound by the latency of its short dependent steps):
+//   A  scores: warp (row group, key group, value range) multiplies its 16 rows by its share of the keys
+//      (mma.sync.m16n8k16, float32 accumulators) and leaves them in shared memory as float32; with 16
+//      warps two share a group of 8 keys, each over half of the `d` values, and step B adds their
+//      partial scores;
+//   B  softmax: threads / rows threads per row: scale, mask, running maximum and sum in float32
 //      (ex2.approx on scores pre-multiplied by log2 e); the weights go back to shared memory as TWO
 //      bfloat16 terms (the rounded weight and what the rounding left over), so that they stay
 //      float32 in effect through the second product;
@@ -26,8 +29,6 @@
 // partial output with its maximum and sum; bfi_attention_latent_bf16 then runs the merge.
 #include "attention_tiles.cuh"
 
-#define AL_WARPS 8
-#define AL_THREADS (AL_WARPS * 32)
 #define AL_PS(KT) ((KT) + 8)      // row stride of the weights' tiles, in bfloat16 (odd in 16-byte chunks)
 #define AL_SS(KT) ((KT) + 1)      // row stride of the score tile, in float32
 #define AL_LOG2E 1.4426950408889634f
@@ -38,8 +39,8 @@ __device__ __forceinline__ float al_gate(const bf16* gate, long gate_stride, lon
     return 1.0f / (1.0f + expf(-x));          // expf(+large) = inf gives 0, expf(-large) = 0 gives 1
 }
 
-template <int RG, int NT, int AL_KEYS>
-__global__ void __launch_bounds__(AL_THREADS, 1)
+template <int RG, int NT, int AL_KEYS, int NW, int DS>
+__global__ void __launch_bounds__(NW * 32, 1)
 attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ out, long out_stride,
                         const bf16* __restrict__ pages, const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
@@ -47,10 +48,11 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                         const float* __restrict__ sinks, const bf16* __restrict__ gate, long gate_stride, int n_splits,
                         float* __restrict__ part_o, float* __restrict__ part_ml) {
     constexpr int QR = 16 * RG;               // query rows of a block
-    constexpr int KG = AL_WARPS / RG;         // key groups in step A
+    constexpr int THREADS = NW * 32;
+    constexpr int KG = NW / (RG * DS);        // key groups in step A (DS warps share one, each with a range of the values)
     constexpr int KW = AL_KEYS / KG;          // keys of a warp in step A
     constexpr int KN = KW / 8;                // its score tiles of 8 keys
-    constexpr int TPR = AL_THREADS / QR;      // threads per row in step B
+    constexpr int TPR = THREADS / QR;      // threads per row in step B
     constexpr int KPT = AL_KEYS / TPR;        // keys per thread in step B
     constexpr int PS = AL_PS(AL_KEYS), SS = AL_SS(AL_KEYS);
     pdl_trigger();
@@ -74,8 +76,8 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     bf16* ks[2] = {qs + QR * dp, qs + QR * dp + AL_KEYS * dp};        // [keys of a tile][dp] each
     bf16* ph = ks[1] + AL_KEYS * dp;                                  // [QR][PS] rounded weights
     bf16* pl = ph + QR * PS;                                       // [QR][PS] what the rounding left over
-    float* ss = reinterpret_cast<float*>(pl + QR * PS);            // [QR][SS] scores
-    float* corr_s = ss + QR * SS;                                  // [QR] factor for the running output
+    float* ss = reinterpret_cast<float*>(pl + QR * PS);            // [DS][QR][SS] scores (DS partial sums each)
+    float* corr_s = ss + DS * QR * SS;                             // [QR] factor for the running output
     float* m_s = corr_s + QR;                                         // [QR] final maximum
     float* l_s = m_s + QR;                                            // [QR] final sum
     __shared__ int tile_ok[2];
@@ -96,7 +98,7 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
         if (threadIdx.x == 0) tile_ok[stage] = page >= 0;
         const bf16* src = pages + ((size_t)(page < 0 ? 0 : page) * BFI_PAGE_TOKENS + (size_t)(kt % PER_PAGE) * AL_KEYS) * d;
         const int key0 = kt * AL_KEYS;
-        for (int row = warp; row < AL_KEYS; row += AL_WARPS) {        // a warp per row, a lane per 16 bytes
+        for (int row = warp; row < AL_KEYS; row += NW) {        // a warp per row, a lane per 16 bytes
             // rows that no query of the block sees may never have been written: zeros, so that a zero
             // weight times a stray NaN cannot reach the output
             const bool live = page >= 0 && key0 + row <= hi_block;
@@ -110,7 +112,7 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
     };
 
     // ---- the block's query rows -> shared memory (rows past the sequence are zero)
-    for (int i = threadIdx.x; i < QR * chunks; i += AL_THREADS) {
+    for (int i = threadIdx.x; i < QR * chunks; i += THREADS) {
         const int row = i / chunks, c = i - row * chunks;
         bf16* dst = qs + row * dp + c * 8;
         const long r = row0 + row;
@@ -139,7 +141,7 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 #pragma unroll
             for (int c = 0; c < 4; ++c) o[a][n][c] = 0.0f;
     const int col0 = warp * 8 * NT;               // first value column of this warp in step C
-    const int rg = warp % RG, kg = warp / RG;     // step A's row group and key group
+    const int rg = warp % RG, kg = (warp / RG) % KG, ds = warp / (RG * KG);     // step A's row group, key group, value range
 
     for (int kt = kt_beg; kt < kt_end; ++kt) {
         const int stage = (kt - kt_beg) & 1;
@@ -157,7 +159,10 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
                 for (int c = 0; c < 4; ++c) s[j][c] = s2[j][c] = 0.0f;
             const bf16* qrow = qs + (rg * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * dp + (lane >> 4) * 8;
             const bf16* krow = ktile + (kg * KW + (lane & 7)) * dp;
-            const int ksteps = d >> 4;
+            // this warp's steps of 16 values: all of them, or one of DS ranges
+            const int per_ds = ((d >> 4) + DS - 1) / DS;
+            const int k_lo = ds * per_ds;
+            const int ksteps = min(d >> 4, k_lo + per_ds);
             // two steps of 16 values per turn; the fragments of the next turn are asked for before this
             // turn's products, so the tensor cores do not wait for shared memory
             uint32_t a0[2][4], a1[2][4], b[2][KN][4];
@@ -170,9 +175,9 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 #pragma unroll
                 for (int j = 0; j < KN; ++j) ldmatrix_x4(b[buf][j], krow + j * 8 * dp + kc * 8);
             };
-            fetch(0, 0);
+            if (k_lo < ksteps) fetch(k_lo, 0);
             int buf = 0;
-            for (int kk = 0; kk < ksteps; kk += 2, buf ^= 1) {
+            for (int kk = k_lo; kk < ksteps; kk += 2, buf ^= 1) {
                 if (kk + 2 < ksteps) {
                     if (buf == 0) fetch(kk + 2, 1);
                     else fetch(kk + 2, 0);
@@ -191,7 +196,7 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
             }
 #pragma unroll
             for (int j = 0; j < KN; ++j) {
-                float* dst = ss + (rg * 16 + g) * SS + kg * KW + j * 8 + 2 * t;
+                float* dst = ss + (ds * QR + rg * 16 + g) * SS + kg * KW + j * 8 + 2 * t;
                 dst[0] = s[j][0] + s2[j][0];
                 dst[1] = s[j][1] + s2[j][1];
                 dst[8 * SS] = s[j][2] + s2[j][2];
@@ -209,7 +214,9 @@ attention_latent_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restr
 #pragma unroll
             for (int i = 0; i < KPT; ++i) {
                 const int key = kt * AL_KEYS + bsub * KPT + i;
-                float x = ss[brow * SS + bsub * KPT + i] * scale_log2;
+                float x = ss[brow * SS + bsub * KPT + i];
+                if (DS == 2) x += ss[(QR + brow) * SS + bsub * KPT + i];
+                x *= scale_log2;
                 if (!ok || key > bpos) x = -INFINITY;
                 v[i] = x;
                 mx = fmaxf(mx, x);
@@ -373,19 +380,21 @@ attention_latent_merge_kernel(const float* __restrict__ part_o, const float* __r
     }
 }
 
-static size_t latent_smem(int rows, int keys, int d) {
+static size_t latent_smem(int rows, int keys, int d, int ds = 1) {
     return (size_t)(rows + 2 * keys) * (d + 8) * sizeof(bf16) + (size_t)2 * rows * AL_PS(keys) * sizeof(bf16) +
-           (size_t)rows * AL_SS(keys) * sizeof(float) + (size_t)3 * rows * sizeof(float);
+           (size_t)ds * rows * AL_SS(keys) * sizeof(float) + (size_t)3 * rows * sizeof(float);
 }
 
-template <int RG, int NT, int KT>
+template <int RG, int NT, int KT, int NW, int DS>
 static int launch_latent(const void* q, long q_stride, void* out, long out_stride, const void* pages, const int* block_table,
                          int table_stride, const int* cu_seqlens, const int* seq_slot, const int* seq_start, int n_seqs,
                          int max_tokens, int heads, int d, int dv, float scale, const float* sinks, const bf16* gate,
                          long gate_stride, int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
     constexpr int QR = 16 * RG;
-    const size_t smem = latent_smem(QR, KT, d);
-    auto kernel = attention_latent_kernel<RG, NT, KT>;
+    static_assert((DS == 1 || DS == 2) && NW % (RG * DS) == 0 && (KT * RG * DS) % (8 * NW) == 0 && (NW * 32) % QR == 0 &&
+                  (KT * QR) % (64 * NW) == 0, "a warp takes whole groups of 8 keys, a thread an even number of keys of its row");
+    const size_t smem = latent_smem(QR, KT, d, DS);
+    auto kernel = attention_latent_kernel<RG, NT, KT, NW, DS>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return bfi_fail("attention_latent: cannot reserve %zu bytes of shared memory: %s", smem,
@@ -393,7 +402,7 @@ static int launch_latent(const void* q, long q_stride, void* out, long out_strid
     }
     const long rows = (long)max_tokens * heads;
     dim3 grid((unsigned)((rows + QR - 1) / QR), n_splits, n_seqs);
-    bfi_launch(kernel, grid, dim3(AL_THREADS), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)pages,
+    bfi_launch(kernel, grid, dim3(NW * 32), smem, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)pages,
                block_table, table_stride, cu_seqlens, seq_slot, seq_start, heads, d, dv, scale * AL_LOG2E, sinks, gate, gate_stride,
                n_splits, part_o, part_ml);
     if (bfi_check_launch("attention_latent")) return 1;
@@ -425,25 +434,27 @@ extern "C" int bfi_attention_latent_bf16(const void* q, long q_stride, void* out
         n_seqs > 65535 || n_splits > 65535)
         return 2;
     if (latent_smem(64, 32, d) > 227 * 1024) return 2;
-#define BFI_AL_CASE(RG, NT)                                                                                               \
-    return launch_latent<RG, NT, (RG == 4 ? 32 : 64)>(q, q_stride, out, out_stride, pages, block_table, table_stride, cu_seqlens, seq_slot,    \
+#define BFI_AL_CASE(RG, NT, KT, NW, DS)                                                                                      \
+    return launch_latent<RG, NT, KT, NW, DS>(q, q_stride, out, out_stride, pages, block_table, table_stride, cu_seqlens, seq_slot, \
                                  seq_start, n_seqs, max_tokens, heads, d, dv, scale, sinks, (const bf16*)gate, gate_stride, n_splits, part_o,   \
                                  part_ml, stream)
-    // few rows: blocks of 16 or 32 rows that take a whole page of keys per turn, where that fits
+    // few rows: blocks of 16 or 32 rows that take a whole page of keys per turn, where that fits.  A
+    // block of 16 rows (single tokens of up to 16 heads) is bound by the latency of its short dependent
+    // steps, so it has 16 warps: two share a group of 8 keys, each over half of the row's values (with
+    // 32 rows the same made no difference: 186 against 181 us at 64 sequences of 4,096 tokens)
     const long rows = (long)max_tokens * heads;
     const bool few = rows <= 32 && latent_smem(32, 64, d) <= 227 * 1024;
-    if (rows <= 16 && latent_smem(16, 64, d) <= 227 * 1024) {
-        if (dv <= 128) BFI_AL_CASE(1, 2);
-        if (dv <= 256) BFI_AL_CASE(1, 4);
-        BFI_AL_CASE(1, 8);
+    if (rows <= 16 && latent_smem(16, 64, d, 2) <= 227 * 1024) {
+        if (dv <= 256) BFI_AL_CASE(1, 2, 64, 16, 2);
+        BFI_AL_CASE(1, 4, 64, 16, 2);
     }
     if (few) {
-        if (dv <= 128) BFI_AL_CASE(2, 2);
-        if (dv <= 256) BFI_AL_CASE(2, 4);
-        BFI_AL_CASE(2, 8);
+        if (dv <= 128) BFI_AL_CASE(2, 2, 64, 8, 1);
+        if (dv <= 256) BFI_AL_CASE(2, 4, 64, 8, 1);
+        BFI_AL_CASE(2, 8, 64, 8, 1);
     }
-    if (dv <= 128) BFI_AL_CASE(4, 2);
-    if (dv <= 256) BFI_AL_CASE(4, 4);
-    BFI_AL_CASE(4, 8);
+    if (dv <= 128) BFI_AL_CASE(4, 2, 32, 8, 1);
+    if (dv <= 256) BFI_AL_CASE(4, 4, 32, 8, 1);
+    BFI_AL_CASE(4, 8, 32, 8, 1);
 #undef BFI_AL_CASE
 }
