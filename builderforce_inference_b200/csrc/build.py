@@ -25,7 +25,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 # streaming weights and the cache at memory speed.
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["errors.cu", "elementwise.cu", "gemm_simt.cu", "attention_paged.cu", "attention_prepare.cu", "lightning.cu",
-             "recurrence.cu", "moe.cu", "latent.cu", "sublayer_out.cu", "sampling.cu", "utility.cu"],
+             "recurrence.cu", "channelwise.cu", "moe.cu", "latent.cu", "sublayer_out.cu", "sampling.cu", "utility.cu"],
     "fast": ["errors.cu", "skinny_gemm.cu", "attention_decode.cu", "attention_prefill.cu", "gemm_tcgen05.cu",
              "attention_prefill_tcgen05.cu", "attention_latent.cu", "weight_stream.cu", "lightning_chunked.cu"],
 }

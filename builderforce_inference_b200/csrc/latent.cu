@@ -204,7 +204,7 @@ template <typename T, typename TW>
 __global__ void __launch_bounds__(LAT_THREADS)
 latent_expand_kernel(const T* __restrict__ lat, long lat_stride, const TW* __restrict__ w_uv, const T* __restrict__ gate,
                      long gate_stride, T* __restrict__ out, long out_stride, const int* __restrict__ token_slot, int n_tokens,
-                     int dv, int rank) {
+                     int dv, int rank, int gate_values) {
     pdl_trigger();
     extern __shared__ float ls[];                 // [LAT_TOK][rank] then [LAT_TOK] gates
     float* gs = ls + LAT_TOK * rank;
@@ -219,7 +219,8 @@ latent_expand_kernel(const T* __restrict__ lat, long lat_stride, const TW* __res
     if (threadIdx.x < LAT_TOK) {
         const int t = t0 + threadIdx.x;
         float g = 1.0f;
-        if (gate != nullptr && t < n_tokens && token_slot[t] >= 0) g = lat_sigmoid(to_f32(gate[(size_t)t * gate_stride + h]));
+        if (gate != nullptr && !gate_values && t < n_tokens && token_slot[t] >= 0)
+            g = lat_sigmoid(to_f32(gate[(size_t)t * gate_stride + h]));
         gs[threadIdx.x] = g;
     }
     __syncthreads();
@@ -241,8 +242,12 @@ latent_expand_kernel(const T* __restrict__ lat, long lat_stride, const TW* __res
 #pragma unroll
             for (int tt = 0; tt < LAT_TOK; ++tt) {
                 const int t = t0 + tt;
-                if (t < n_tokens && token_slot[t] >= 0)
-                    out[(size_t)t * out_stride + (size_t)h * dv + i] = from_f32<T>(acc[tt] * gs[tt]);
+                if (t < n_tokens && token_slot[t] >= 0) {
+                    float g = gs[tt];
+                    if (gate != nullptr && gate_values)      // a gate per value, laid out like the output
+                        g = lat_sigmoid(to_f32(gate[(size_t)t * gate_stride + (size_t)h * dv + i]));
+                    out[(size_t)t * out_stride + (size_t)h * dv + i] = from_f32<T>(acc[tt] * g);
+                }
             }
         }
     }
@@ -250,7 +255,7 @@ latent_expand_kernel(const T* __restrict__ lat, long lat_stride, const TW* __res
 
 extern "C" int bfi_latent_expand(const void* lat, int dtype, long lat_stride, const void* w_uv, int w_dtype, const void* gate,
                                  long gate_stride, void* out, long out_stride, const int* token_slot, int n_tokens, int n_heads,
-                                 int dv, int rank, cudaStream_t stream) {
+                                 int dv, int rank, int gate_values, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype), "latent_expand: unknown dtype code");
     BFI_REQUIRE(n_heads > 0 && n_heads <= 65535 && dv > 0 && rank > 0, "latent_expand: bad sizes");
     BFI_REQUIRE(dtype == w_dtype || w_dtype == BFI_F32, "latent_expand: weights of the activations' type or float32");
@@ -262,13 +267,13 @@ extern "C" int bfi_latent_expand(const void* lat, int dtype, long lat_stride, co
     BFI_REQUIRE(grid.z <= 65535, "latent_expand: heads of %d values are too large", dv);
     if (dtype == BFI_F32)
         bfi_launch(latent_expand_kernel<float, float>, grid, dim3(LAT_THREADS), smem, stream, (const float*)lat, lat_stride,
-                   (const float*)w_uv, (const float*)gate, gate_stride, (float*)out, out_stride, token_slot, n_tokens, dv, rank);
+                   (const float*)w_uv, (const float*)gate, gate_stride, (float*)out, out_stride, token_slot, n_tokens, dv, rank, gate_values);
     else if (w_dtype == BFI_F32)
         bfi_launch(latent_expand_kernel<bf16, float>, grid, dim3(LAT_THREADS), smem, stream, (const bf16*)lat, lat_stride,
-                   (const float*)w_uv, (const bf16*)gate, gate_stride, (bf16*)out, out_stride, token_slot, n_tokens, dv, rank);
+                   (const float*)w_uv, (const bf16*)gate, gate_stride, (bf16*)out, out_stride, token_slot, n_tokens, dv, rank, gate_values);
     else
         bfi_launch(latent_expand_kernel<bf16, bf16>, grid, dim3(LAT_THREADS), smem, stream, (const bf16*)lat, lat_stride,
-                   (const bf16*)w_uv, (const bf16*)gate, gate_stride, (bf16*)out, out_stride, token_slot, n_tokens, dv, rank);
+                   (const bf16*)w_uv, (const bf16*)gate, gate_stride, (bf16*)out, out_stride, token_slot, n_tokens, dv, rank, gate_values);
     return bfi_check_launch("latent_expand");
 }
 

@@ -14,8 +14,8 @@
 // Column j of S, and with it value j of o, depends on no other column, so a block owns a range of
 // columns of one head of one sequence and walks the sequence's new tokens in order.
 //
-// bfi_causal_conv: a short causal convolution per channel over the step's tokens with silu, whose
-// last taps-1 inputs per sequence are kept as state (zero before the first token).
+// bfi_causal_conv: a short causal convolution per channel over the step's tokens (with silu or
+// without), whose last taps-1 inputs per sequence are kept as state (zero before the first token).
 // bfi_gated_group_norm: the gate and the norm in equal parts that follow such a recurrence.
 #include "common.cuh"
 
@@ -530,20 +530,40 @@ extern "C" int bfi_decay_scan(const void* qk, long qk_stride, int q_off, int k_o
 }
 
 // ------------------------------------------------------------------------------------------
-// Causal convolution per channel with silu.  Token t of a sequence reads its own input and the
-// taps-1 before it: rows of this step while they belong to the same sequence, then the kept
-// inputs of earlier steps (state [slots][taps-1][C], oldest first; zero when the slot was taken,
-// which is what stands before a sequence's first token).
-//     y[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] * u[t-j, c])
-// conv_forward_kernel computes y; conv_keep_kernel then moves the state on (it must not run
-// before every y of the step has read the old state: it is a launch of its own).  When every
+// Causal convolution per channel.  Token t of a sequence reads its own input and the taps-1
+// before it: rows of this step while they belong to the same sequence, then the kept inputs of
+// earlier steps (state [slots][taps-1][C], oldest first; zero when the slot was taken, which is
+// what stands before a sequence's first token).
+//     y[t, c] = act(bias[c] + sum_j w[c, taps-1-j] * u[t-j, c])      act: silu (1) or none (0)
+// Options, each a pointer or flag that may be absent:
+//   add_input   y[t, c] += u[t, c]  (the convolution as a correction of its own input)
+//   copy        copy[t, c] = u[t, c] in the output type (the input itself, for a reader beside the
+//               convolution that wants it in the product's type)
+//   mix         for channels c >= mix_off, with e = c - mix_off:
+//                   mix_src:  y[t, c] = (1 - lambda) y[t, c] + lambda mix_src[t, e]
+//                   mix_dst:  mix_dst[t, e] = y[t, c]       (after the mixing, when both are there)
+//               lambda is one float32 on the device.
+// The input may be float32 while the output is bfloat16 (a convolution straight off the residual
+// stream).  conv_forward_kernel computes y; conv_keep_kernel then moves the state on (it must not
+// run before every y of the step has read the old state: it is a launch of its own).  When every
 // sequence brings one token, one thread does both for its channel.
 // ------------------------------------------------------------------------------------------
-template <typename T>
-__global__ void conv_forward_kernel(const T* __restrict__ u, long u_stride, int u_off, const void* __restrict__ w,
+struct ConvExtras {
+    int act, add_input;
+    void* copy;
+    long copy_stride;
+    int mix_off;
+    const void* mix_src;
+    void* mix_dst;
+    long mix_stride;
+    const float* mix_lambda;
+};
+
+template <typename TI, typename TO>
+__global__ void conv_forward_kernel(const TI* __restrict__ u, long u_stride, int u_off, const void* __restrict__ w,
                                     const void* __restrict__ bias, int w_dtype, float* __restrict__ state,
-                                    T* __restrict__ y, long y_stride, const int* __restrict__ token_slot, int C, int taps,
-                                    int fused_keep) {
+                                    TO* __restrict__ y, long y_stride, const int* __restrict__ token_slot, int C, int taps,
+                                    int fused_keep, const ConvExtras x) {
     pdl_trigger();
     pdl_wait();
     const int t = blockIdx.x;
@@ -560,7 +580,18 @@ __global__ void conv_forward_kernel(const T* __restrict__ u, long u_stride, int 
                          : st[(size_t)(taps - 1 + own - j) * C];
         acc = fmaf(load_as_f32(w, w_dtype, (size_t)ch * taps + (taps - 1 - j)), in[j], acc);
     }
-    y[(size_t)t * y_stride + ch] = from_f32<T>(rec_silu(acc));
+    if (x.act) acc = rec_silu(acc);
+    if (x.add_input) acc += in[0];
+    if (ch >= x.mix_off) {
+        const size_t e = (size_t)t * x.mix_stride + (ch - x.mix_off);
+        if (x.mix_src != nullptr) {
+            const float lam = *x.mix_lambda;
+            acc = (1.0f - lam) * acc + lam * to_f32(reinterpret_cast<const TO*>(x.mix_src)[e]);
+        }
+        if (x.mix_dst != nullptr) reinterpret_cast<TO*>(x.mix_dst)[e] = from_f32<TO>(acc);
+    }
+    y[(size_t)t * y_stride + ch] = from_f32<TO>(acc);
+    if (x.copy != nullptr) reinterpret_cast<TO*>(x.copy)[(size_t)t * x.copy_stride + ch] = from_f32<TO>(in[0]);
     if (fused_keep)                                // one token per sequence: the window moves on by one
         for (int i = 0; i < taps - 1; ++i) st[(size_t)i * C] = in[taps - 2 - i];
 }
@@ -585,23 +616,36 @@ __global__ void conv_keep_kernel(const T* __restrict__ u, long u_stride, int u_o
 }
 
 extern "C" int bfi_causal_conv(const void* u, long u_stride, int u_off, int dtype, const void* w, const void* bias,
-                               int w_dtype, float* state, void* y, long y_stride, const int* token_slot,
+                               int w_dtype, float* state, void* y, long y_stride, int y_dtype, const int* token_slot,
                                const int* cu_seqlens, const int* seq_slot, int n_tokens, int n_seqs, int C, int taps,
-                               int single_tokens, cudaStream_t stream) {
-    BFI_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype), "causal_conv: unknown dtype code");
+                               int single_tokens, int act, int add_input, void* copy, long copy_stride, int mix_off,
+                               const void* mix_src, void* mix_dst, long mix_stride, const float* mix_lambda,
+                               cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(dtype) && dtype_ok(w_dtype) && dtype_ok(y_dtype), "causal_conv: unknown dtype code");
+    BFI_REQUIRE(dtype == y_dtype || dtype == BFI_F32, "causal_conv: the output has the input's type, or the input is float32");
     BFI_REQUIRE(C > 0 && taps >= 1 && taps <= REC_MAX_TAPS, "causal_conv: %d channels, %d taps (at most %d)", C, taps, REC_MAX_TAPS);
     BFI_REQUIRE(u_stride >= u_off + C && y_stride >= C, "causal_conv: row stride shorter than the channels");
+    BFI_REQUIRE(copy == nullptr || copy_stride >= C, "causal_conv: the copy's row stride is shorter than the channels");
+    const bool mixes = mix_src != nullptr || mix_dst != nullptr;
+    BFI_REQUIRE(!mixes || (mix_off >= 0 && mix_off < C && mix_stride >= C - mix_off && (mix_src == nullptr || mix_lambda != nullptr)),
+                "causal_conv: the mixed channels need rows of their count and, to mix, the factor");
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
     const int threads = 128;
     const dim3 grid_t(n_tokens, (C + threads - 1) / threads), grid_s(n_seqs, (C + threads - 1) / threads);
     BFI_REQUIRE(grid_t.y <= 65535, "causal_conv: %d channels are too many for one launch", C);
     const int fused = single_tokens ? 1 : 0;
-    if (dtype == BFI_F32)
-        bfi_launch(conv_forward_kernel<float>, grid_t, dim3(threads), 0, stream, (const float*)u, u_stride, u_off, w, bias, w_dtype,
-                   state, (float*)y, y_stride, token_slot, C, taps, fused);
+    ConvExtras x;
+    x.act = act, x.add_input = add_input, x.copy = copy, x.copy_stride = copy_stride;
+    x.mix_off = mixes ? mix_off : C, x.mix_src = mix_src, x.mix_dst = mix_dst, x.mix_stride = mix_stride, x.mix_lambda = mix_lambda;
+    if (dtype == BFI_F32 && y_dtype == BFI_F32)
+        bfi_launch(conv_forward_kernel<float, float>, grid_t, dim3(threads), 0, stream, (const float*)u, u_stride, u_off, w, bias,
+                   w_dtype, state, (float*)y, y_stride, token_slot, C, taps, fused, x);
+    else if (dtype == BFI_F32)
+        bfi_launch(conv_forward_kernel<float, bf16>, grid_t, dim3(threads), 0, stream, (const float*)u, u_stride, u_off, w, bias,
+                   w_dtype, state, (bf16*)y, y_stride, token_slot, C, taps, fused, x);
     else
-        bfi_launch(conv_forward_kernel<bf16>, grid_t, dim3(threads), 0, stream, (const bf16*)u, u_stride, u_off, w, bias, w_dtype,
-                   state, (bf16*)y, y_stride, token_slot, C, taps, fused);
+        bfi_launch(conv_forward_kernel<bf16, bf16>, grid_t, dim3(threads), 0, stream, (const bf16*)u, u_stride, u_off, w, bias,
+                   w_dtype, state, (bf16*)y, y_stride, token_slot, C, taps, fused, x);
     int rc = bfi_check_launch("causal_conv");
     if (rc || fused || taps == 1) return rc;
     if (dtype == BFI_F32)

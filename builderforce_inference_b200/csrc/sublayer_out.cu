@@ -1,7 +1,8 @@
 // What happens to a sublayer's output on its way into the residual stream when the block does more
 // than add it: a norm of the output before the add, and a weighted sum of two outputs.
 //
-//   bfi_norm_add:      x[t, :] += y[t, :] * rsqrt(mean(y[t, :]^2) + eps) * w        (y float32)
+//   bfi_norm_add:      x[t, :] += mult * y'[t, :] * rsqrt(mean(y'[t, :]^2) + eps) * w   (y float32)
+//                      with y' = y, or, given gate logits g (and a bias b), y' = y * sigmoid(g + b)
 //                      and, when asked, the next sublayer's norm of the new x in the same kernel:
 //                      h[t, :] = x[t, :] * rsqrt(mean(x[t, :]^2) + eps2) * w2       (h in the activation dtype)
 //   bfi_weighted_sum:  out[t, :] = a * y0[t, :] + b * y1[t, :]                      (all float32)
@@ -12,22 +13,52 @@
 // float32 or bfloat16.  All arithmetic is float32.
 #include "common.cuh"
 
+struct NormAddGate {
+    const void* logits;       // null: no gate
+    int dtype;
+    long stride;
+    const void* bias;         // null: none
+    int bias_dtype;
+};
+
+__device__ __forceinline__ float out_sigmoid(float x) {
+    if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
+    const float z = expf(x);
+    return z / (1.0f + z);
+}
+
 __global__ void norm_add_kernel(float* __restrict__ x, long x_stride, const float* __restrict__ y, long y_stride,
                                 const void* __restrict__ w, int w_dtype, int width, float eps, const void* __restrict__ w2,
-                                int w2_dtype, float eps2, void* __restrict__ h, int h_dtype, long h_stride) {
+                                int w2_dtype, float eps2, void* __restrict__ h, int h_dtype, long h_stride, float mult,
+                                const NormAddGate g) {
     pdl_trigger();
     pdl_wait();
     __shared__ float scratch[33];
     const int t = blockIdx.x;
     const float* yr = y + (size_t)t * y_stride;
     float* xr = x + (size_t)t * x_stride;
+    const bool gated = g.logits != nullptr;
     float ss = 0.0f;
-    for (int j = threadIdx.x; j < width; j += blockDim.x) ss = fmaf(yr[j], yr[j], ss);
+    for (int j = threadIdx.x; j < width; j += blockDim.x) {
+        float v = yr[j];
+        if (gated) {
+            float z = load_as_f32(g.logits, g.dtype, (size_t)t * g.stride + j);
+            if (g.bias) z += load_as_f32(g.bias, g.bias_dtype, j);
+            v *= out_sigmoid(z);
+        }
+        ss = fmaf(v, v, ss);
+    }
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
     float ss2 = 0.0f;
     for (int j = threadIdx.x; j < width; j += blockDim.x) {
-        const float v = xr[j] + yr[j] * scale * load_as_f32(w, w_dtype, j);
+        float yv = yr[j];
+        if (gated) {
+            float z = load_as_f32(g.logits, g.dtype, (size_t)t * g.stride + j);
+            if (g.bias) z += load_as_f32(g.bias, g.bias_dtype, j);
+            yv *= out_sigmoid(z);
+        }
+        const float v = xr[j] + mult * (yv * scale * load_as_f32(w, w_dtype, j));
         xr[j] = v;
         ss2 = fmaf(v, v, ss2);
     }
@@ -41,15 +72,21 @@ __global__ void norm_add_kernel(float* __restrict__ x, long x_stride, const floa
 
 extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stride, const void* w, int w_dtype,
                             int n_rows, int width, float eps, const void* w2, int w2_dtype, float eps2, void* h,
-                            int h_dtype, long h_stride, cudaStream_t stream) {
-    BFI_REQUIRE(dtype_ok(w_dtype) && dtype_ok(w2_dtype) && dtype_ok(h_dtype), "norm_add: unknown dtype code");
+                            int h_dtype, long h_stride, float mult, const void* gate, int gate_dtype, long gate_stride,
+                            const void* gate_bias, int gate_bias_dtype, cudaStream_t stream) {
+    BFI_REQUIRE(dtype_ok(w_dtype) && dtype_ok(w2_dtype) && dtype_ok(h_dtype) && dtype_ok(gate_dtype) && dtype_ok(gate_bias_dtype),
+                "norm_add: unknown dtype code");
     BFI_REQUIRE(n_rows >= 0 && width > 0, "norm_add: bad sizes rows=%d width=%d", n_rows, width);
     BFI_REQUIRE(x_stride >= width && y_stride >= width, "norm_add: row stride shorter than the row");
     BFI_REQUIRE(h == nullptr || (w2 != nullptr && h_stride >= width), "norm_add: the next norm needs its weight and rows of the width");
+    BFI_REQUIRE(gate == nullptr || gate_stride >= width, "norm_add: the gate's row stride is shorter than the row");
     if (n_rows == 0) return 0;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    NormAddGate g;
+    g.logits = gate, g.dtype = gate_dtype, g.stride = gate_stride, g.bias = gate != nullptr ? gate_bias : nullptr;
+    g.bias_dtype = gate_bias_dtype;
     bfi_launch(norm_add_kernel, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, eps, w2,
-               w2_dtype, eps2, h, h_dtype, h_stride);
+               w2_dtype, eps2, h, h_dtype, h_stride, mult, g);
     return bfi_check_launch("norm_add");
 }
 

@@ -70,7 +70,7 @@ class Decoder:
 
     # ---- what the cache has to provide -----------------------------------------------
     def run_needs(self) -> List[Any]:
-        return [self.blocks[r.layer].mixer().cache_need() for r in self.spec.schedule]
+        return [self.blocks[r.layer].cache_need() for r in self.spec.schedule]
 
     def run_cache_of(self) -> List[Optional[int]]:
         return [r.cache_of for r in self.spec.schedule]

@@ -399,7 +399,8 @@ def latent_expand(lat: torch.Tensor, w_uv: torch.Tensor, gate: Optional[torch.Te
                   token_slot: torch.Tensor, n_heads: int, v_dim: int, rank: int) -> None:
     """``out[t, h] = (W_uv_h lat[t, h]) * sigmoid(gate[t, h])`` with ``w_uv`` ``[heads * v_dim, rank]``,
     ``lat`` ``[tokens, heads * rank]`` (the attention's weighted sums of cached latents) and ``gate`` a
-    view ``[tokens, heads]`` of logits (None: no gate)."""
+    view ``[tokens, heads]`` of logits (None: no gate), or ``[tokens, heads * v_dim]``: a gate per
+    output value."""
     _need_cuda(lat, w_uv, gate, out, token_slot)
     _rows_2d(lat, "latent outputs")
     _rows_2d(out, "head outputs")
@@ -411,11 +412,12 @@ def latent_expand(lat: torch.Tensor, w_uv: torch.Tensor, gate: Optional[torch.Te
         raise KernelError("latent_expand: [tokens, heads * rank] in, [tokens, heads * v_dim] out, of one dtype")
     if gate is not None:
         _rows_2d(gate, "gate logits")
-        if gate.shape != (n, n_heads) or gate.dtype != lat.dtype:
-            raise KernelError("latent_expand: the gate must be [tokens, heads] of the activations' dtype")
+        if gate.shape not in ((n, n_heads), (n, n_heads * v_dim)) or gate.dtype != lat.dtype:
+            raise KernelError("latent_expand: the gate must be [tokens, heads] or [tokens, heads * v_dim] of the activations' dtype")
     library("core").call("bfi_latent_expand", _ptr(lat), c_int(dtype_code(lat.dtype)), c_long(lat.stride(0)), _ptr(w_uv),
                          c_int(dtype_code(w_uv.dtype)), _ptr(gate), c_long(0 if gate is None else gate.stride(0)), _ptr(out),
-                         c_long(out.stride(0)), _ptr(token_slot), c_int(n), c_int(n_heads), c_int(v_dim), c_int(rank), _stream())
+                         c_long(out.stride(0)), _ptr(token_slot), c_int(n), c_int(n_heads), c_int(v_dim), c_int(rank),
+                         c_int(1 if gate is not None and v_dim > 1 and gate.shape[1] == n_heads * v_dim else 0), _stream())
 
 
 def bigram_add(table: torch.Tensor, ids: torch.Tensor, token_pos: torch.Tensor, token_slot: torch.Tensor,
@@ -454,11 +456,22 @@ def _f32_vector(t: Optional[torch.Tensor], n: int, what: str) -> None:
 
 
 def norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, next_w: Optional[torch.Tensor] = None,
-             next_eps: float = 0.0, out: Optional[torch.Tensor] = None) -> None:
-    """``x[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w``: a sublayer's output, normed, into the
-    float32 residual stream.  With ``next_w`` and ``out`` the next sublayer's norm of the new ``x`` is
-    made in the same kernel: ``out[t] = x[t] * rsqrt(mean(x[t]^2) + next_eps) * next_w``."""
-    _need_cuda(x, y, w, next_w, out)
+             next_eps: float = 0.0, out: Optional[torch.Tensor] = None, mult: float = 1.0,
+             gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> None:
+    """``x[t] += mult * y[t] * rsqrt(mean(y[t]^2) + eps) * w``: a sublayer's output, normed, into the
+    float32 residual stream.  With ``gate`` (logits ``[rows, width]`` of either storage type, and an
+    optional ``gate_bias`` ``[width]``) ``y`` is first multiplied by ``sigmoid(gate + gate_bias)``.
+    With ``next_w`` and ``out`` the next sublayer's norm of the new ``x`` is made in the same
+    kernel: ``out[t] = x[t] * rsqrt(mean(x[t]^2) + next_eps) * next_w``."""
+    _need_cuda(x, y, w, next_w, out, gate, gate_bias)
+    if gate is not None:
+        _rows_2d(gate, "gate logits")
+        if gate.shape != x.shape:
+            raise KernelError("norm_add: the gate's logits must have the residual stream's shape")
+        if gate_bias is not None and (gate_bias.shape != (x.shape[1],) or not gate_bias.is_contiguous()):
+            raise KernelError(f"norm_add: the gate's bias must be [{x.shape[1]}]")
+    elif gate_bias is not None:
+        raise KernelError("norm_add: a gate bias without gate logits")
     if (next_w is None) != (out is None):
         raise KernelError("norm_add: the next norm needs both its weight and its output")
     if out is not None:
@@ -475,7 +488,9 @@ def norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, next
                          c_int(dtype_code(w.dtype)), c_int(x.shape[0]), c_int(x.shape[1]), c_float(eps), _ptr(next_w),
                          c_int(0 if next_w is None else dtype_code(next_w.dtype)), c_float(next_eps), _ptr(out),
                          c_int(0 if out is None else dtype_code(out.dtype)), c_long(0 if out is None else out.stride(0)),
-                         _stream())
+                         c_float(mult), _ptr(gate), c_int(0 if gate is None else dtype_code(gate.dtype)),
+                         c_long(0 if gate is None else gate.stride(0)), _ptr(gate_bias),
+                         c_int(0 if gate_bias is None else dtype_code(gate_bias.dtype)), _stream())
 
 
 def weighted_sum(out: torch.Tensor, y0: torch.Tensor, a: float, y1: torch.Tensor, b: float) -> None:
@@ -566,13 +581,24 @@ def decay_scan(qk: torch.Tensor, q_off: int, k_off: int, v: torch.Tensor, v_off:
                          _ptr(chunk_decay), _stream())
 
 
+CONV_ACT_NONE, CONV_ACT_SILU = 0, 1
+
+
 def causal_conv(u: torch.Tensor, u_off: int, channels: int, w: torch.Tensor, bias: Optional[torch.Tensor],
                 state: torch.Tensor, y: torch.Tensor, token_slot: torch.Tensor, cu_seqlens: torch.Tensor,
-                seq_slot: torch.Tensor, n_seqs: int, single_tokens: bool = False) -> None:
-    """``y[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] u[t-j, u_off + c])`` within each sequence; the
+                seq_slot: torch.Tensor, n_seqs: int, single_tokens: bool = False, act: int = CONV_ACT_SILU,
+                add_input: bool = False, copy: Optional[torch.Tensor] = None, mix_off: int = 0,
+                mix_src: Optional[torch.Tensor] = None, mix_dst: Optional[torch.Tensor] = None,
+                mix_lambda: Optional[torch.Tensor] = None) -> None:
+    """``y[t, c] = act(bias[c] + sum_j w[c, taps-1-j] u[t-j, u_off + c])`` within each sequence; the
     inputs before a step's first token come from ``state`` (float32 ``[slots, taps-1, channels]``,
-    oldest first), which is then moved on by the step's tokens."""
-    _need_cuda(u, w, bias, state, y, token_slot, cu_seqlens, seq_slot)
+    oldest first), which is then moved on by the step's tokens.  ``act`` is silu or none;
+    ``add_input`` adds ``u[t]`` to the result; ``copy`` receives ``u[t]`` itself in the output's type.
+    The input may be float32 with a bfloat16 output.  For channels from ``mix_off`` on, ``mix_src``
+    (rows of ``channels - mix_off`` values in the output's type) is mixed in as
+    ``(1 - lambda) y + lambda mix_src`` with ``mix_lambda`` one float32 on the device, and
+    ``mix_dst`` receives the resulting values."""
+    _need_cuda(u, w, bias, state, y, token_slot, cu_seqlens, seq_slot, copy, mix_src, mix_dst, mix_lambda)
     _rows_2d(u, "convolution input")
     _rows_2d(y, "convolution output")
     _i32(token_slot, "token slots")
@@ -583,14 +609,101 @@ def causal_conv(u: torch.Tensor, u_off: int, channels: int, w: torch.Tensor, bia
         raise KernelError(f"causal_conv: weights must be contiguous [{channels}, taps]")
     if bias is not None and (bias.shape != (channels,) or bias.dtype != w.dtype or not bias.is_contiguous()):
         raise KernelError(f"causal_conv: bias must be [{channels}] of the weights' dtype")
-    if u.dtype != y.dtype or y.shape != (u.shape[0], channels) or u_off + channels > u.shape[1]:
-        raise KernelError("causal_conv: input and output must share a dtype; output [tokens, channels]")
+    if (u.dtype != y.dtype and u.dtype != torch.float32) or y.shape != (u.shape[0], channels) or u_off + channels > u.shape[1]:
+        raise KernelError("causal_conv: the output has the input's dtype (or the input is float32); output [tokens, channels]")
     if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (max(taps - 1, 0), channels):
         raise KernelError("causal_conv: the state must be contiguous float32 [slots, taps-1, channels]")
+    if copy is not None:
+        _rows_2d(copy, "copy of the convolution's input")
+        if copy.shape != y.shape or copy.dtype != y.dtype:
+            raise KernelError("causal_conv: the copy must have the output's shape and dtype")
+    mix_stride = 0
+    for m in (mix_src, mix_dst):
+        if m is not None:
+            _rows_2d(m, "mixed channels")
+            if m.shape != (u.shape[0], channels - mix_off) or m.dtype != y.dtype or mix_off < 0:
+                raise KernelError(f"causal_conv: mixed channels must be [tokens, {channels - mix_off}] of the output's dtype")
+            if mix_stride not in (0, m.stride(0)):
+                raise KernelError("causal_conv: the two mixed buffers must share a row stride")
+            mix_stride = m.stride(0)
+    if mix_src is not None:
+        _f32_vector(mix_lambda, 1, "causal_conv: the mixing factor")
+        if mix_lambda is None:
+            raise KernelError("causal_conv: mixing needs its factor")
     library("core").call("bfi_causal_conv", _ptr(u), c_long(u.stride(0)), c_int(u_off), c_int(dtype_code(u.dtype)),
                          _ptr(w), _ptr(bias), c_int(dtype_code(w.dtype)), _ptr(state), _ptr(y), c_long(y.stride(0)),
-                         _ptr(token_slot), _ptr(cu_seqlens), _ptr(seq_slot), c_int(u.shape[0]), c_int(n_seqs),
-                         c_int(channels), c_int(taps), c_int(1 if single_tokens else 0), _stream())
+                         c_int(dtype_code(y.dtype)), _ptr(token_slot), _ptr(cu_seqlens), _ptr(seq_slot), c_int(u.shape[0]),
+                         c_int(n_seqs), c_int(channels), c_int(taps), c_int(1 if single_tokens else 0), c_int(act),
+                         c_int(1 if add_input else 0), _ptr(copy), c_long(0 if copy is None else copy.stride(0)),
+                         c_int(mix_off), _ptr(mix_src), _ptr(mix_dst), c_long(mix_stride), _ptr(mix_lambda), _stream())
+
+
+SCAN_CAND_IDENTITY, SCAN_CAND_POSITIVE = 0, 1
+
+
+def gated_scan(proj: torch.Tensor, z_off: int, u_off: int, g_off: Optional[int], channels: int,
+               z_bias: Optional[torch.Tensor], u_bias: Optional[torch.Tensor], y: torch.Tensor, state: torch.Tensor,
+               cu_seqlens: torch.Tensor, seq_slot: torch.Tensor, n_seqs: int, max_seq_tokens: int,
+               cand: int = SCAN_CAND_POSITIVE) -> None:
+    """A recurrence with one float32 state value per channel: with ``z = sigmoid(proj[z] + z_bias)``
+    and ``u = proj[u] + u_bias``, ``S_t = (1 - z_t) S_(t-1) + z_t cand(u_t)`` and
+    ``y_t = S_t * silu(proj[g])`` (``g_off`` None: ``y_t = S_t``).  ``cand`` is the identity or the
+    positive map (``u + 1/2`` for ``u >= 0``, ``sigmoid(u)`` below).  ``state`` is ``[slots, channels]``
+    and is moved on; ``max_seq_tokens`` (the most tokens a sequence brings) sizes the split over time."""
+    _need_cuda(proj, z_bias, u_bias, y, state, cu_seqlens, seq_slot)
+    _rows_2d(proj, "projections")
+    _rows_2d(y, "recurrence output")
+    _i32(cu_seqlens, "cu_seqlens")
+    _i32(seq_slot, "sequence slots")
+    _f32_vector(z_bias, channels, "gated_scan: the gate's bias")
+    _f32_vector(u_bias, channels, "gated_scan: the candidate's bias")
+    if y.dtype != proj.dtype or y.shape != (proj.shape[0], channels):
+        raise KernelError("gated_scan: the output must be [tokens, channels] of the projections' dtype")
+    if max(z_off, u_off, -1 if g_off is None else g_off) + channels > proj.shape[1] or min(z_off, u_off) < 0:
+        raise KernelError("gated_scan: a column range lies outside the projections")
+    if state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (channels,):
+        raise KernelError("gated_scan: the state must be contiguous float32 [slots, channels]")
+    library("core").call("bfi_gated_scan", _ptr(proj), c_long(proj.stride(0)), c_int(z_off), c_int(u_off),
+                         c_int(-1 if g_off is None else g_off), c_int(dtype_code(proj.dtype)), _ptr(z_bias), _ptr(u_bias),
+                         _ptr(y), c_long(y.stride(0)), _ptr(state), _ptr(cu_seqlens), _ptr(seq_slot), c_int(n_seqs),
+                         c_int(channels), c_int(cand), c_int(max_seq_tokens), _stream())
+
+
+def bias_act(u: torch.Tensor, bias: Optional[torch.Tensor], y: torch.Tensor, fill: Optional[torch.Tensor] = None,
+             fill_bias: Optional[torch.Tensor] = None) -> None:
+    """``y[t, j] = gelu_tanh(u[t, j] + bias[j])`` over rows of one storage type; with ``fill`` (float32
+    rows) and ``fill_bias``, ``fill[t, :] = fill_bias`` in the same launch: the bias of a product that
+    then accumulates into those rows."""
+    _need_cuda(u, bias, y, fill, fill_bias)
+    _rows_2d(u, "activation input")
+    _rows_2d(y, "activation output")
+    if y.shape != u.shape or y.dtype != u.dtype:
+        raise KernelError("bias_act: input and output of one shape and dtype")
+    if bias is not None and (bias.shape != (u.shape[1],) or not bias.is_contiguous()):
+        raise KernelError(f"bias_act: the bias must be [{u.shape[1]}]")
+    if (fill is None) != (fill_bias is None):
+        raise KernelError("bias_act: rows to fill come with their bias")
+    if fill is not None:
+        _rows_2d(fill, "rows to fill")
+        if fill.dtype != torch.float32 or fill.shape[0] != u.shape[0] or fill_bias.shape != (fill.shape[1],) \
+                or not fill_bias.is_contiguous():
+            raise KernelError("bias_act: the rows to fill are float32 [rows, n] and their bias [n]")
+    library("core").call("bfi_bias_act", _ptr(u), c_long(u.stride(0)), c_int(dtype_code(u.dtype)), _ptr(bias),
+                         c_int(0 if bias is None else dtype_code(bias.dtype)), _ptr(y), c_long(y.stride(0)), c_int(u.shape[0]),
+                         c_int(u.shape[1]), _ptr(fill), c_long(0 if fill is None else fill.stride(0)), _ptr(fill_bias),
+                         c_int(0 if fill_bias is None else dtype_code(fill_bias.dtype)),
+                         c_int(0 if fill is None else fill.shape[1]), _stream())
+
+
+def sigmoid_gate(x: torch.Tensor, g: torch.Tensor, group: int) -> None:
+    """``x[t, j] *= sigmoid(g[t, j // group])`` in place, over rows of one storage type."""
+    _need_cuda(x, g)
+    _rows_2d(x, "rows to gate")
+    _rows_2d(g, "gate logits")
+    if group < 1 or x.shape[1] % group != 0 or g.shape != (x.shape[0], x.shape[1] // group) or g.dtype != x.dtype:
+        raise KernelError("sigmoid_gate: logits [rows, cols / group] of the rows' dtype")
+    library("core").call("bfi_sigmoid_gate", _ptr(x), c_long(x.stride(0)), _ptr(g), c_long(g.stride(0)),
+                         c_int(dtype_code(x.dtype)), c_int(x.shape[0]), c_int(x.shape[1]), c_int(group), _stream())
 
 
 GATE_SIGMOID, GATE_SILU = 0, 1

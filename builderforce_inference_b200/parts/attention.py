@@ -21,7 +21,15 @@ the keys of its own block of ``chunk`` consecutive positions, blocks counted fro
 ``out_bias`` (whether the output projection carries a bias when the others do; default: it does);
 ``exact_weights`` (the softmax's weights stay float32 up to the second product, also in a bfloat16
 run: the tensor-core prompt kernel then multiplies with two bfloat16 terms per weight);
-the position encoding's pairing and partial width.  The plain
+the position encoding's pairing and partial width; ``conv_taps`` (a short causal convolution over
+time on every channel of q, k and v, directly after the projection and before norm and rotation,
+without bias or activation; the last ``taps - 1`` projected rows are kept per sequence, so the mixer
+then asks the cache for a fixed-size state beside its pages); ``v_mix`` (``"source"``: the values of
+this layer, as they are cached, are also left in a buffer of the step; ``"mix"``: the values become
+``(1 - lambda) v + lambda v_source`` with the source layer's values of the same token and a learned
+number ``lambda``, before they are cached; both ride on the convolution's kernel); ``gate``
+(``"head"``: head a's output is multiplied by ``sigmoid(W_g h)_a``, the logits coming out of the same
+product as q, k and v).  The plain
 combination (no bias, head norm or none, own values, rotate-half) runs the per-head kernel that
 fuses norm, rotation and cache write; the others run the per-token kernel that also adds the
 biases, so no variant costs a launch of its own.
@@ -35,7 +43,7 @@ import torch
 
 from ..kernels import ops
 from ..kernels.linear import EPI_ACCUMULATE, EPI_STORE, linear
-from .base import MIXERS, POSITION_ENCODINGS, KVNeed, Mixer, ParamSpec, PartSpec
+from .base import MIXERS, POSITION_ENCODINGS, KVNeed, Mixer, ParamSpec, PartSpec, StateNeed
 
 
 @MIXERS.register("attention")
@@ -46,7 +54,8 @@ class Attention(Mixer):
                  position: Optional[PartSpec] = None, qk_norm=False, eps: float = 1e-6,
                  window: Optional[int] = None, scale: Optional[float] = None, own_kv: bool = True,
                  bias: bool = False, values: str = "projection", sink=None, v_dim: Optional[int] = None,
-                 chunk: Optional[int] = None, out_bias: Optional[bool] = None, exact_weights: bool = False):
+                 chunk: Optional[int] = None, out_bias: Optional[bool] = None, exact_weights: bool = False,
+                 conv_taps: Optional[int] = None, v_mix: Optional[str] = None, gate: Optional[str] = None):
         if n_heads % n_kv_heads != 0:
             raise ValueError(f"GQA: {n_heads} query heads do not divide into {n_kv_heads} kv heads")
         if head_dim % 2 != 0 or head_dim > 512:
@@ -70,6 +79,17 @@ class Attention(Mixer):
             raise ValueError("values that are the keys have the keys' size")
         if not (sink is None or sink == "learned" or isinstance(sink, (int, float))):
             raise ValueError(f"sink must be a number or 'learned', got {sink!r}")
+        if conv_taps is not None and not 1 <= conv_taps <= 16:
+            raise ValueError(f"the convolution on q, k and v takes 1 to 16 taps, got {conv_taps}")
+        if v_mix not in (None, "source", "mix"):
+            raise ValueError(f"v_mix must be 'source' or 'mix', got {v_mix!r}")
+        if v_mix is not None and (conv_taps is None or not own_kv or values == "keys"):
+            raise ValueError("value mixing rides on the convolution of a layer's own q, k and v")
+        if gate not in (None, "head"):
+            raise ValueError(f"gate must be 'head', got {gate!r}")
+        if conv_taps is not None and not own_kv:
+            raise ValueError("a layer that borrows its keys has no convolution on q, k and v")
+        self.taps, self.v_mix, self.gate = (None if conv_taps is None else int(conv_taps)), v_mix, gate
         self.width, self.n_heads, self.n_kv_heads, self.head_dim = width, n_heads, n_kv_heads, head_dim
         self.qk_norm, self.eps, self.window = (qk_norm or None), float(eps), window
         self.bias, self.values_are_keys = bool(bias), values == "keys"
@@ -98,6 +118,14 @@ class Attention(Mixer):
                 specs["v_proj"] = ParamSpec((self.n_kv_heads * self.v_dim, h))
         if self.learned_sink:
             specs["sink"] = ParamSpec((self.n_heads,), "matrix")
+        if self.taps is not None:
+            for name in ("q_proj", "k_proj", "v_proj"):
+                if name in specs:
+                    specs[name + ".conv"] = ParamSpec((specs[name].shape[0], self.taps))
+        if self.v_mix is not None:
+            specs["v_mix"] = ParamSpec((), "matrix")       # the source layer's is stored too, and unused
+        if self.gate:
+            specs["g_proj"] = ParamSpec((self.n_heads, h))
         if self.qk_norm:
             row = self.qk_norm == "row"
             specs["q_norm"] = ParamSpec((self.n_heads * d if row else d,), "norm")
@@ -115,8 +143,16 @@ class Attention(Mixer):
             and getattr(self.position, "pairing", "half") == "half" and self.v_dim == self.head_dim
 
     def cache_need(self):
-        return KVNeed(self.n_kv_heads, self.head_dim, self.window,
-                      v_dim=None if self.v_dim == self.head_dim else self.v_dim, chunk=self.chunk)
+        kv = KVNeed(self.n_kv_heads, self.head_dim, self.window,
+                    v_dim=None if self.v_dim == self.head_dim else self.v_dim, chunk=self.chunk)
+        if self.taps is None or self.taps == 1:
+            return kv
+        return (kv, StateNeed((self.taps - 1, self._n_qkv()), "float32"))
+
+    def _n_qkv(self) -> int:
+        """Columns of q, k and v together in the projection."""
+        n_kv_in = self.n_kv_heads if self.own_kv else 0
+        return (self.n_heads + n_kv_in) * self.head_dim + (0 if self.values_are_keys else n_kv_in * self.v_dim)
 
     def prepare(self, runtime, max_positions: int) -> None:
         self.position.prepare(runtime, max_positions)
@@ -125,6 +161,16 @@ class Attention(Mixer):
         mats = [tensors["q_proj"]]
         if self.own_kv:
             mats += [tensors["k_proj"]] + ([] if self.values_are_keys else [tensors["v_proj"]])
+        if self.taps is not None:
+            convs = [tensors[n + ".conv"] for n in ("q_proj", "k_proj", "v_proj") if n + ".conv" in tensors]
+            if len({c.dtype for c in convs}) > 1:
+                convs = [c.float() for c in convs]
+            self.conv_w = torch.cat(convs, dim=0).contiguous()
+            self.no_history = torch.empty((1, 0, self.conv_w.shape[0]), dtype=torch.float32, device=runtime.device)
+        if self.v_mix == "mix":
+            self.mix_lambda = tensors["v_mix"].float().reshape(1).contiguous()
+        if self.gate:
+            mats.append(tensors["g_proj"])      # the gate's logits come out of the same product, behind q, k and v
         if len({m.dtype for m in mats}) > 1:
             mats = [m.float() for m in mats]
         self.w_qkv = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
@@ -158,8 +204,24 @@ class Attention(Mixer):
         if run.writes_cache != self.own_kv:
             raise RuntimeError("an attention layer writes the cache exactly when it has k and v projections")
         d = self.head_dim
-        qkv = ctx.rows("attn.qkv", (self.n_heads + n_kv_in) * d + (0 if self.values_are_keys else n_kv_in * self.v_dim))
-        linear(h, self.w_qkv, qkv, EPI_STORE)
+        n_qkv = self._n_qkv()
+        proj = ctx.rows("attn.qkv", self.w_qkv.shape[0])
+        linear(h, self.w_qkv, proj, EPI_STORE)
+        qkv = proj if proj.shape[1] == n_qkv else proj[:, :n_qkv]
+        if self.taps is not None:
+            kept = run.state if self.taps > 1 else self.no_history
+            if kept is None:
+                raise RuntimeError("the convolution on q, k and v needs its per-sequence state")
+            conv = ctx.rows("attn.conv", n_qkv)
+            n_v = n_kv_in * self.v_dim
+            shared = ctx.rows("attn.v_source", n_v) if self.v_mix else None
+            ops.causal_conv(proj, 0, n_qkv, self.conv_w, None, kept, conv, ctx.token_slot, ctx.cu_seqlens, ctx.seq_slot,
+                            ctx.n_seqs, single_tokens=ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs,
+                            act=ops.CONV_ACT_NONE, mix_off=n_qkv - n_v,
+                            mix_src=shared if self.v_mix == "mix" else None,
+                            mix_dst=shared if self.v_mix == "source" else None,
+                            mix_lambda=self.mix_lambda if self.v_mix == "mix" else None)
+            qkv = conv
 
         fused = self.position.fused_rotary()
         write = ops.FLAG_WRITE_CACHE if run.writes_cache else 0
@@ -191,6 +253,8 @@ class Attention(Mixer):
 
         out = ctx.rows("attn.out", self.n_heads * self.v_dim)
         self.attend(ctx, qkv, out, kv)
+        if self.gate:
+            ops.sigmoid_gate(out, proj[:, n_qkv:n_qkv + self.n_heads], self.v_dim)
         linear(out, self.w_o, residual, epilogue)
 
     def attend(self, ctx, qkv, out, kv) -> None:

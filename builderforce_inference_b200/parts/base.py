@@ -192,6 +192,11 @@ class Block(Part):
     def mixer(self) -> Mixer:
         raise NotImplementedError
 
+    def cache_need(self):
+        """What a run of the block keeps per sequence: its mixer's needs, followed by what the block
+        keeps itself (none, for most).  ``run.entries`` then carries them in this order."""
+        return self.mixer().cache_need()
+
     def forward(self, ctx, residual, run) -> None:
         raise NotImplementedError
 

@@ -10,10 +10,25 @@ the mixer's and the feed-forward's last matrix product.
               The sublayers write their output to a float32 buffer (``forward_store``) and the
               second norm adds it, normed, into the residual stream in one kernel, which also makes
               the feed-forward's input norm.
+``outnorm``   a norm on each sublayer's OUTPUT only; the sublayers read the residual stream itself:
+              ``x += mult * norm1(g1 * mixer(c1(x))); x += mult * norm2(g2 * ffn(c2(x)))``.  ``c`` is the
+              identity or, with ``conv_taps``, ``c(x)_t = x_t + sum_j w[:, j] x_(t - taps + 1 + j)``, a
+              causal convolution over time per channel whose last ``taps - 1`` inputs are kept per
+              sequence (the block asks the cache for them beside what its mixer keeps); ``g`` is 1 or,
+              with ``gate``, ``sigmoid(W_g x + b_g)`` element by element, made from the residual stream
+              as it stands before the convolution.  One kernel reads the float32 stream and writes
+              both the convolved and the plain copy in the activation dtype; one kernel gates, norms,
+              scales and adds the sublayer's float32 output.  The feed-forward (with its norm,
+              convolution and gate) may be absent.
 """
 from __future__ import annotations
 
-from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, PartSpec
+from typing import Dict
+
+from ..cache.cache import KVView, RunCache, needs_of
+from ..kernels import ops
+from ..kernels.linear import EPI_STORE, linear
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, ParamSpec, PartSpec, StateNeed
 
 
 @BLOCKS.register("prenorm")
@@ -107,3 +122,105 @@ class SandwichBlock(Block):
         h = self.norm1b.add_to(ctx, residual, y, then=self.norm2)      # the add and the next norm in one kernel
         self.ffn.forward_store(ctx, h, y)
         self.norm2b.add_to(ctx, residual, y)
+
+
+@BLOCKS.register("outnorm")
+class OutNormBlock(Block):
+    graph_safe = True
+
+    def __init__(self, width: int, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec = None, ffn: PartSpec = None,
+                 mult: float = 1.0, conv_taps: int = None, gate: bool = False):
+        if (ffn is None) != (norm2 is None):
+            raise ValueError("an out-norm block has a feed-forward with its norm, or neither")
+        if conv_taps is not None and not 1 <= conv_taps <= 16:
+            raise ValueError(f"an out-norm block's input convolution takes 1 to 16 taps, got {conv_taps}")
+        self.width, self.mult = int(width), float(mult)
+        self.taps = None if conv_taps is None else int(conv_taps)
+        self.has_gate = bool(gate)
+        self.norm1 = NORMS.build(norm1)
+        self._mixer = MIXERS.build(mixer)
+        self.norm2 = NORMS.build(norm2) if ffn is not None else None
+        self.ffn = FEED_FORWARDS.build(ffn) if ffn is not None else None
+        self.n_sub = 1 if self.ffn is None else 2
+        self.conv_w = [None, None]
+        self.gate_w = [None, None]
+        self.gate_b = [None, None]
+        self.no_history = None
+
+    def children(self):
+        out = {"norm1": self.norm1, "mixer": self._mixer}
+        if self.ffn is not None:
+            out.update({"norm2": self.norm2, "ffn": self.ffn})
+        return out
+
+    def mixer(self):
+        return self._mixer
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = {}
+        for i in range(1, self.n_sub + 1):
+            if self.taps is not None:
+                specs[f"conv{i}"] = ParamSpec((self.width, self.taps))
+            if self.has_gate:
+                specs[f"gate{i}_proj"] = ParamSpec((self.width, self.width))
+                specs[f"gate{i}_proj.bias"] = ParamSpec((self.width,))
+        return specs
+
+    def load(self, tensors, runtime) -> None:
+        for i in range(self.n_sub):
+            if self.taps is not None:
+                self.conv_w[i] = tensors[f"conv{i + 1}"].contiguous()
+            if self.has_gate:
+                self.gate_w[i] = tensors[f"gate{i + 1}_proj"]
+                self.gate_b[i] = tensors[f"gate{i + 1}_proj.bias"].contiguous()
+        import torch
+        self.no_history = torch.empty((1, 0, self.width), dtype=torch.float32, device=runtime.device)
+
+    def _own_needs(self) -> tuple:
+        if self.taps is None or self.taps == 1:
+            return ()
+        return (StateNeed((self.taps - 1, self.width), "float32"),) * self.n_sub
+
+    def cache_need(self):
+        return needs_of(self._mixer.cache_need()) + self._own_needs()
+
+    def _input(self, ctx, x, i: int, kept):
+        """What sublayer ``i`` reads (convolved) and what its gate reads (plain), in the activation dtype."""
+        import torch
+        h = ctx.rows("block.in", self.width)
+        plain = ctx.rows("block.plain", self.width) if self.has_gate else None
+        if self.taps is None:
+            h.copy_(x)
+            return h, h
+        single = ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs
+        ops.causal_conv(x, 0, self.width, self.conv_w[i], None, kept, h, ctx.token_slot, ctx.cu_seqlens, ctx.seq_slot,
+                        ctx.n_seqs, single_tokens=single, act=ops.CONV_ACT_NONE, add_input=True, copy=plain)
+        return h, plain
+
+    def _output(self, ctx, x, y, plain, i: int, norm) -> None:
+        glog = None
+        if self.has_gate:
+            glog = ctx.rows("block.gate", self.width)
+            linear(plain, self.gate_w[i], glog, EPI_STORE)
+        norm.add_to(ctx, x, y, mult=self.mult, gate=glog, gate_bias=self.gate_b[i])
+
+    def forward(self, ctx, residual, run) -> None:
+        import torch
+        if not run.writes_cache:
+            raise RuntimeError("an out-norm block keeps its convolutions' inputs: its run needs a cache of its own")
+        own = self._own_needs()
+        n_mixer = len(run.entries) - len(own)
+        entries = tuple(run.entries[:n_mixer])
+        kept = list(run.entries[n_mixer:]) if own else [self.no_history] * self.n_sub
+        kv = next((e for e in entries if isinstance(e, KVView)), None)
+        state = next((e for e in entries if not isinstance(e, KVView)), None)
+        mixer_run = RunCache(kv=kv, state=state, writes_cache=True, entries=entries)
+        y = ctx.rows("sublayer.out", self.width, torch.float32)
+        h, plain = self._input(ctx, residual, 0, kept[0])
+        self._mixer.forward_store(ctx, h, y, mixer_run)
+        self._output(ctx, residual, y, plain, 0, self.norm1)
+        if self.ffn is None:
+            return
+        h, plain = self._input(ctx, residual, 1, kept[1])
+        self.ffn.forward_store(ctx, h, y)
+        self._output(ctx, residual, y, plain, 1, self.norm2)

@@ -23,6 +23,15 @@ over the whole row), then projected.
 a decay per key channel ``a = sigmoid(W_a2 (W_a1 h) + b_a2)^(1/tau)``, ``c = 1``, no skip.  Every
 head's output is normed over ``vdim`` (one weight of ``vdim`` values for all heads), multiplied by
 ``silu(W_g h)`` and projected.
+
+``min_gru`` keeps ONE value per channel instead of a matrix per head (``kernels/ops.gated_scan``): with
+``z = sigmoid(W_z h + b_z)`` and ``u = W_x h + b_x`` of ``inner`` values each,
+
+    S_t = (1 - z_t) S_(t-1) + z_t cand(u_t)        out_t = W_o (S_t * silu(W_g h_t))
+
+where ``cand(u) = u + 1/2`` for ``u >= 0`` and ``sigmoid(u)`` below (``candidate="positive"``), or ``u``
+itself (``"identity"``).  Its gates read the current token only, so the recurrence is linear in S
+and the kernel cuts a sequence's tokens into segments that run side by side.
 """
 from __future__ import annotations
 
@@ -187,4 +196,55 @@ class GatedLinearAttention(Mixer):
                        **_chunking(ctx, self.n_heads * self.dim * self.vdim, self.n_heads * self.dim))
         y = ctx.rows("gla.y", vv)
         ops.gated_group_norm(o, proj[:, 2 * qk + vv:2 * qk + 2 * vv], self.norm, self.eps, y, self.n_heads, gate_first=False)
+        linear(y, self.w_o, target, epilogue)
+
+
+@MIXERS.register("min_gru")
+class MinGRU(Mixer):
+    graph_safe = True
+
+    def __init__(self, width: int, inner: int, candidate: str = "positive", bias: bool = True):
+        if inner < 1:
+            raise ValueError(f"minGRU: bad size inner={inner}")
+        if candidate not in ("positive", "identity"):
+            raise ValueError(f"minGRU: the candidate is 'positive' or 'identity', got {candidate!r}")
+        self.width, self.inner, self.bias = int(width), int(inner), bool(bias)
+        self.cand = ops.SCAN_CAND_POSITIVE if candidate == "positive" else ops.SCAN_CAND_IDENTITY
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        n, w = self.inner, self.width
+        specs = {"z_proj": ParamSpec((n, w)), "x_proj": ParamSpec((n, w)), "g_proj": ParamSpec((n, w)),
+                 "o_proj": ParamSpec((w, n))}
+        if self.bias:
+            specs.update({"z_proj.bias": ParamSpec((n,)), "x_proj.bias": ParamSpec((n,))})
+        return specs
+
+    def cache_need(self):
+        return StateNeed((self.inner,), "float32")
+
+    def load(self, tensors, runtime) -> None:
+        mats = [tensors[n] for n in ("z_proj", "x_proj", "g_proj")]
+        if len({m.dtype for m in mats}) > 1:
+            mats = [m.float() for m in mats]
+        self.w_in = torch.cat(mats, dim=0).contiguous()      # one product gives the gate, the candidate and the output gate
+        self.w_o = tensors["o_proj"]
+        self.b_z = _as_f32(tensors["z_proj.bias"]) if self.bias else None
+        self.b_x = _as_f32(tensors["x_proj.bias"]) if self.bias else None
+
+    def forward(self, ctx, h, residual, run) -> None:
+        self._run(ctx, h, residual, run, EPI_ACCUMULATE)
+
+    def forward_store(self, ctx, h, out, run) -> None:
+        self._run(ctx, h, out, run, EPI_STORE)
+
+    def _run(self, ctx, h, target, run, epilogue) -> None:
+        state = run.state
+        if state is None or not run.writes_cache:
+            raise RuntimeError("a minGRU needs a state of its own for its run")
+        n = self.inner
+        proj = ctx.rows("gru.proj", 3 * n)
+        linear(h, self.w_in, proj, EPI_STORE)
+        y = ctx.rows("gru.y", n)
+        ops.gated_scan(proj, 0, n, 2 * n, n, self.b_z, self.b_x, y, state, ctx.cu_seqlens, ctx.seq_slot, ctx.n_seqs,
+                       ctx.max_seq_tokens, cand=self.cand)
         linear(y, self.w_o, target, epilogue)

@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its model.
 
 A config.json names its architecture under ``architectures[0]`` (a class name such as
-``Qwen3ForCausalLM``), ``model_type`` (``qwen3``) or ``architecture`` (``Datasun``, ``Bepilorn``, ``Munerax``).  Any of them selects the entry; the lookup is
+``Qwen3ForCausalLM``), ``model_type`` (``qwen3``) or ``architecture`` (``Datasun``, ``Bepilorn``, ``Munerax``, ``Kikelorn``).  Any of them selects the entry; the lookup is
 exact and case-sensitive, and an unknown name is answered with the list of known ones, as in
 the reference (crates/bfi-models/src/arch.rs:70-91).
 """
@@ -78,6 +78,10 @@ def _register_builtin() -> None:
     from .config.munerax import MuneraxConfig
     register_architecture(("Munerax", "munerax"),
                           Architecture(name="munerax", config_class=MuneraxConfig, describe=munerax.describe))
+    from .architectures import kikelorn
+    from .config.kikelorn import KikelornConfig
+    register_architecture(("Kikelorn", "kikelorn"),
+                          Architecture(name="kikelorn", config_class=KikelornConfig, describe=kikelorn.describe))
 
 
 _register_builtin()
