@@ -81,8 +81,8 @@ def test_round_trip_through_to_dict():
 
 
 def test_registry_names_and_unknown_architecture():
-    assert registered_architectures() == ["Bepilorn", "Datasun", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun", "munerax",
-                                          "qwen3"]
+    assert registered_architectures() == ["Bepilorn", "Datasun", "Kikelorn", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun",
+                                          "kikelorn", "munerax", "qwen3"]
     assert architecture_for({"model_type": "qwen3"}).name == "qwen3"
     assert architecture_for({"architectures": ["Qwen3ForCausalLM"]}).name == "qwen3"
     with pytest.raises(ConfigError) as e:
