@@ -23,7 +23,10 @@ layer sizes, a few sizes, random weights: a 2,048-token prompt with its breakdow
 and decode at batch 8 and 64 behind 1,024-token prompts.  One line.  ``--design bepilorn`` does
 the same for the Bepilorn design (three state-space layers to one pair of chunked sink attention
 and gated linear attention, a routed feed-forward) beside Datasun and Qwen3, with the milliseconds
-of every kernel of a prompt step and of a single-token step.
+of every kernel of a prompt step and of a single-token step.  ``--design munerax`` and
+``--design kikelorn`` do it for those designs (Kikelorn: chunked attention, latent attention with a
+query latent, a minGRU and chunked attention again, in out-norm blocks) beside the designs closest
+to them and Qwen3.
 
 The work is one GPU's: for ``--gpus`` above 1 it says so and exits with 2.  The reference arm
 (``--impl reference``) is unavailable: the reference is a Rust workspace, there is no Rust
@@ -379,6 +382,27 @@ def munerax_config(width, heads, kv, d, ff, layers):
             "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": out}
 
 
+KIKELORN_TAPS = 4              # taps of the convolutions in the design runs, in front of the sublayers and on q, k, v
+
+
+def kikelorn_config(width, heads, kv, d, ff, layers):
+    """A Kikelorn model of these layer sizes: of every four layers the first and the last are
+    chunked attention (values of the keys' size, four taps on q, k and v, values mixed with the first
+    layer's), the second is latent attention as Munerax's in these runs (a cache row of 512 + d/2
+    values) with a query latent of 3/8 of the width, the third a minGRU of 3/2 of the width; a dense
+    feed-forward with biases in every layer."""
+    half = d // 2
+    att = {"heads": heads, "kv_heads": kv, "dim": d, "vdim": d, "conv": KIKELORN_TAPS, "scale": d ** -0.5,
+           "mask": {"size": DESIGN_WINDOW}, "rot": {"base": 1e6, "dims": half}, "v_mix": True}
+    lat = {"heads": heads, "dim": half, "rot_dim": half, "vdim": d, "kv_rank": MUNERAX_LATENT, "q_rank": 3 * width // 8,
+           "scale": d ** -0.5, "rot": {"base": 1e6, "dims": half, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    gru = {"width": 3 * width // 2}
+    kinds = [("attention", att), ("latent_attention", lat), ("mingru", gru), ("attention", att)]
+    return {"architecture": "Kikelorn", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+            "residual_mult": 0.7, "canon": {"taps": KIKELORN_TAPS},
+            "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]}
+
+
 def decode_breakdown(model, batch, ctx_len):
     """One instrumented single-token step (no graph, an event around every kernel) behind prompts of
     ``ctx_len`` tokens: milliseconds by kernel."""
@@ -412,7 +436,13 @@ def design_run(a) -> int:
         width, heads, kv, d, ff = DESIGN_SIZES[name]
         qwen3 = dict(CONFIG_4B, num_hidden_layers=layers, hidden_size=width, num_attention_heads=heads,
                      num_key_value_heads=kv, head_dim=d, intermediate_size=ff, vocab_size=DESIGN_VOCAB)
-        if a.design == "munerax":       # beside the routed design and beside the dense softmax-attention one
+        if a.design == "kikelorn":      # beside the design with the same latent attention, the one with chunked attention and a recurrence, and the dense one
+            configs = {"kikelorn": kikelorn_config(width, heads, kv, d, ff, layers),
+                       "munerax": munerax_config(width, heads, kv, d, ff, layers),
+                       "bepilorn": bepilorn_config(width, heads, kv, d, ff, layers), "qwen3": qwen3}
+            if a.only:
+                configs = {k: v for k, v in configs.items() if k in a.only.split(",")}
+        elif a.design == "munerax":     # beside the routed design and beside the dense softmax-attention one
             configs = {"munerax": munerax_config(width, heads, kv, d, ff, layers),
                        "bepilorn": bepilorn_config(width, heads, kv, d, ff, layers), "qwen3": qwen3}
         elif a.design == "bepilorn":    # beside the closest design the package has, and beside the dense one
@@ -422,7 +452,7 @@ def design_run(a) -> int:
             configs = {"datasun": datasun_config(width, heads, kv, d, ff, layers), "qwen3": qwen3}
         for design, cfg in configs.items():
             model = Model.from_random(cfg, seed=0, dtype="bfloat16", max_tokens=64 * 2048, max_seq_len=CONTEXT, max_batch=64)
-            by_kernel = a.design in ("bepilorn", "munerax")
+            by_kernel = a.design in ("bepilorn", "munerax", "kikelorn")
             pf = prefill_run(model, PREFILL_TOKENS, 5, layers, breakdown=True, by_kernel=by_kernel)
             row = {"prefill_2048": {"ms": round(pf["ms"], 3), "tok_s": round(pf["tok_s"], 1), "breakdown": pf["breakdown"]}}
             for b in (8, 64):
@@ -439,8 +469,12 @@ def design_run(a) -> int:
                "bepilorn": "state space x3, chunked attention (chunk %d) + gated linear attention x1; %d experts, 4 used, and a shared one"
                            % (DESIGN_WINDOW, BEPILORN_EXPERTS),
                "munerax": "latent attention (cache row %d + head/2) x4, the fourth reading the third's cache; dense feed-forward in "
-                          "layer 0, then %d experts, 4 used, and a shared one" % (MUNERAX_LATENT, BEPILORN_EXPERTS)}[a.design]
-    beside = {"bepilorn": "datasun and qwen3", "munerax": "bepilorn and qwen3"}.get(a.design, "qwen3")
+                          "layer 0, then %d experts, 4 used, and a shared one" % (MUNERAX_LATENT, BEPILORN_EXPERTS),
+               "kikelorn": "chunked attention (chunk %d, %d taps on q, k, v), latent attention (cache row %d + head/2, query latent), "
+                           "minGRU, chunked attention; out-norm blocks with %d taps in front of every sublayer and a gate behind it; "
+                           "dense feed-forward with biases" % (DESIGN_WINDOW, KIKELORN_TAPS, MUNERAX_LATENT, KIKELORN_TAPS)}[a.design]
+    beside = {"bepilorn": "datasun and qwen3", "munerax": "bepilorn and qwen3",
+              "kikelorn": "munerax, bepilorn and qwen3"}.get(a.design, "qwen3")
     print(json.dumps({"workloads": a.design + " beside " + beside
                       + " at equal layer sizes, builder-run beside the benchmark", "dtype": "bf16",
                       "layers": layers, "pattern": pattern, "vocab": DESIGN_VOCAB,
@@ -831,9 +865,10 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers of the same sizes")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
-    ap.add_argument("--design", default=None, choices=["datasun", "bepilorn", "munerax"],
+    ap.add_argument("--design", default=None, choices=["datasun", "bepilorn", "munerax", "kikelorn"],
                     help="instead of the benchmark: this design beside qwen3 at equal layer sizes (see design_run)")
     ap.add_argument("--sizes", default=None, help="with --design: names of DESIGN_SIZES, comma-separated (default: all)")
+    ap.add_argument("--only", default=None, help="with --design kikelorn: the designs to run, comma-separated (default: all four)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

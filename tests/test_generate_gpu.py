@@ -147,7 +147,8 @@ def test_model_exposes_the_step_function_the_slots_and_its_configuration():
     assert isinstance(cfg, Qwen3Config) and cfg.head_dim == 32 and cfg.num_key_value_heads == 3
     with pytest.raises(Exception):
         cfg.head_dim = 64                                   # read-only
-    assert registry() == ["Bepilorn", "Datasun", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun", "munerax", "qwen3"]
+    assert registry() == ["Bepilorn", "Datasun", "Kikelorn", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun", "kikelorn",
+                                          "munerax", "qwen3"]
     assert (model.n_layer(), model.n_vocab(), model.n_ctx(), model.n_embd()) == (3, 384, 256, 96)
     folder = model_folder("B", torch.float32)
     p = random_prompts(384, [9], seed=1)[0]

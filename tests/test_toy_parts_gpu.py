@@ -182,7 +182,8 @@ def test_toy_architecture_with_state_repeated_layers_and_a_shared_cache():
     finally:
         undo()
     from builderforce_inference_b200 import registered_architectures
-    assert registered_architectures() == ["Bepilorn", "Datasun", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun", "munerax", "qwen3"]
+    assert registered_architectures() == ["Bepilorn", "Datasun", "Kikelorn", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun", "kikelorn",
+                                          "munerax", "qwen3"]
 
 
 # ------------------------------------------------------------------------------------------------
@@ -392,7 +393,8 @@ def test_toy_architecture_with_routing_another_position_encoding_and_another_nor
     finally:
         undo()
     from builderforce_inference_b200 import registered_architectures
-    assert registered_architectures() == ["Bepilorn", "Datasun", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun", "munerax", "qwen3"]
+    assert registered_architectures() == ["Bepilorn", "Datasun", "Kikelorn", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun", "kikelorn",
+                                          "munerax", "qwen3"]
 
 
 # ------------------------------------------------------------------------------------------------
@@ -540,4 +542,5 @@ def test_toy_mixer_with_keys_and_values_and_a_state_of_its_own():
     finally:
         undo()
     from builderforce_inference_b200 import registered_architectures
-    assert registered_architectures() == ["Bepilorn", "Datasun", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun", "munerax", "qwen3"]
+    assert registered_architectures() == ["Bepilorn", "Datasun", "Kikelorn", "Munerax", "Qwen3ForCausalLM", "bepilorn", "datasun", "kikelorn",
+                                          "munerax", "qwen3"]
