@@ -20,7 +20,7 @@
 
 #define SCAN_CAND_IDENTITY 0
 #define SCAN_CAND_POSITIVE 1
-#define SCAN_MAX_WARPS 16
+#define SCAN_MAX_WARPS 32
 
 __device__ __forceinline__ float cw_sigmoid(float x) {
     if (x >= 0.0f) return 1.0f / (1.0f + expf(-x));
@@ -36,18 +36,28 @@ struct ScanArgs {
     const int *cu_seqlens, *seq_slot;
 };
 
+// float32 arithmetic in both; with bfloat16 projections the exponential and the division are the hardware's
+// approximations (a few units in the last place of a float32, far below what the projections' rounding left)
 template <typename T>
-__device__ __forceinline__ void scan_coefficients(const T* __restrict__ row, const ScanArgs& a, int ch, float bz, float bu,
-                                                  float& keep, float& add) {
-    const float z = cw_sigmoid(to_f32(row[a.z_off + ch]) + bz);
-    const float u = to_f32(row[a.u_off + ch]) + bu;
-    const float cand = a.cand == SCAN_CAND_POSITIVE ? (u >= 0.0f ? u + 0.5f : cw_sigmoid(u)) : u;
+__device__ __forceinline__ float scan_sigmoid(float x) { return cw_sigmoid(x); }
+template <>
+__device__ __forceinline__ float scan_sigmoid<bf16>(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
+
+template <typename T>
+__device__ __forceinline__ void scan_coefficients(float z_raw, float u_raw, int cand_kind, float bz, float bu, float& keep,
+                                                  float& add) {
+    const float z = scan_sigmoid<T>(z_raw + bz);
+    const float u = u_raw + bu;
+    const float cand = cand_kind == SCAN_CAND_POSITIVE ? (u >= 0.0f ? u + 0.5f : scan_sigmoid<T>(u)) : u;
     keep = 1.0f - z;
     add = z * cand;
 }
 
+#define SCAN_UNROLL 8       // tokens whose inputs are in flight before the chain of multiply-adds walks them
+
 template <typename T>
-__global__ void gated_scan_kernel(const T* __restrict__ proj, T* __restrict__ y, float* __restrict__ state, const ScanArgs a) {
+__global__ void __launch_bounds__(32 * SCAN_MAX_WARPS)
+gated_scan_kernel(const T* __restrict__ proj, T* __restrict__ y, float* __restrict__ state, const ScanArgs a) {
     pdl_trigger();
     __shared__ float seg_a[SCAN_MAX_WARPS][32], seg_b[SCAN_MAX_WARPS][32];
     const int seq = blockIdx.x;
@@ -62,13 +72,26 @@ __global__ void gated_scan_kernel(const T* __restrict__ proj, T* __restrict__ y,
     const int t0 = a.cu_seqlens[seq], nt = a.cu_seqlens[seq + 1] - t0;
     const int per = (nt + n_w - 1) / n_w;
     const int first = min(nt, w * per), last = min(nt, first + per);
+    const T* base = proj + (size_t)t0 * a.p_stride + ch;
     float A = 1.0f, B = 0.0f;
     if (n_w > 1 && live) {
-        for (int t = first; t < last; ++t) {
-            float keep, add;
-            scan_coefficients(proj + (size_t)(t0 + t) * a.p_stride, a, ch, bz, bu, keep, add);
-            B = fmaf(keep, B, add);
-            A *= keep;
+        for (int t = first; t < last; t += SCAN_UNROLL) {
+            float zr[SCAN_UNROLL], ur[SCAN_UNROLL];
+#pragma unroll
+            for (int i = 0; i < SCAN_UNROLL; ++i) {
+                const T* row = base + (size_t)min(t + i, last - 1) * a.p_stride;
+                zr[i] = to_f32(row[a.z_off]);
+                ur[i] = to_f32(row[a.u_off]);
+            }
+#pragma unroll
+            for (int i = 0; i < SCAN_UNROLL; ++i) {
+                if (t + i < last) {
+                    float keep, add;
+                    scan_coefficients<T>(zr[i], ur[i], a.cand, bz, bu, keep, add);
+                    B = fmaf(keep, B, add);
+                    A *= keep;
+                }
+            }
         }
     }
     seg_a[w][lane] = A;
@@ -77,17 +100,26 @@ __global__ void gated_scan_kernel(const T* __restrict__ proj, T* __restrict__ y,
     if (!live) return;
     float S = state[(size_t)slot * a.C + ch];
     for (int i = 0; i < w; ++i) S = fmaf(seg_a[i][lane], S, seg_b[i][lane]);
-    for (int t = first; t < last; ++t) {
-        const T* row = proj + (size_t)(t0 + t) * a.p_stride;
-        float keep, add;
-        scan_coefficients(row, a, ch, bz, bu, keep, add);
-        S = fmaf(keep, S, add);
-        float out = S;
-        if (a.g_off >= 0) {
-            const float g = to_f32(row[a.g_off + ch]);
-            out *= g * cw_sigmoid(g);
+    for (int t = first; t < last; t += SCAN_UNROLL) {
+        float zr[SCAN_UNROLL], ur[SCAN_UNROLL], gr[SCAN_UNROLL];
+#pragma unroll
+        for (int i = 0; i < SCAN_UNROLL; ++i) {
+            const T* row = base + (size_t)min(t + i, last - 1) * a.p_stride;
+            zr[i] = to_f32(row[a.z_off]);
+            ur[i] = to_f32(row[a.u_off]);
+            gr[i] = a.g_off >= 0 ? to_f32(row[a.g_off]) : 0.0f;
         }
-        y[(size_t)(t0 + t) * a.y_stride + ch] = from_f32<T>(out);
+#pragma unroll
+        for (int i = 0; i < SCAN_UNROLL; ++i) {
+            if (t + i < last) {
+                float keep, add;
+                scan_coefficients<T>(zr[i], ur[i], a.cand, bz, bu, keep, add);
+                S = fmaf(keep, S, add);
+                float out = S;
+                if (a.g_off >= 0) out *= gr[i] * scan_sigmoid<T>(gr[i]);
+                y[(size_t)(t0 + t + i) * a.y_stride + ch] = from_f32<T>(out);
+            }
+        }
     }
     if (w == n_w - 1) state[(size_t)slot * a.C + ch] = S;     // the last warp's end is the sequence's
 }
@@ -101,7 +133,7 @@ extern "C" int bfi_gated_scan(const void* proj, long p_stride, int z_off, int u_
     BFI_REQUIRE(p_stride >= z_off + C && p_stride >= u_off + C && p_stride >= g_off + C && y_stride >= C,
                 "gated_scan: row stride shorter than the channels");
     if (n_seqs <= 0) return 0;
-    int warps = (max_seq_tokens + 15) / 16;        // segments of at least 16 tokens
+    int warps = (max_seq_tokens + 15) / 16;        // segments of at least 16 tokens, as many as a block has warps
     if (warps < 1) warps = 1;
     if (warps > SCAN_MAX_WARPS) warps = SCAN_MAX_WARPS;
     const dim3 grid(n_seqs, (C + 31) / 32), block(32, warps);
@@ -133,6 +165,57 @@ __global__ void bias_act_kernel(const T* __restrict__ u, long u_stride, const vo
     if (fill != nullptr && j < fill_cols) fill[(size_t)t * fill_stride + j] = load_as_f32(fill_bias, fb_dtype, j);
 }
 
+// 0.5 z (1 + tanh(y)) = z * sigmoid(2 y), with the hardware's exponential and division (the matrix products' gated
+// epilogue evaluates it the same way for bfloat16)
+__device__ __forceinline__ float gelu_tanh_fast(float g) {
+    const float y = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return __fdividef(g, 1.0f + __expf(-2.0f * y));
+}
+
+// bfloat16 rows whose columns come in whole groups of 8: a thread takes 16 bytes of a row (and, of the rows to
+// fill, the 8 float32 values at the same columns, in as many turns as the wider of the two needs)
+__global__ void bias_act_vec_kernel(const bf16* __restrict__ u, long u_stride, const void* __restrict__ bias, int b_dtype,
+                                    bf16* __restrict__ y, long y_stride, int cols, float* __restrict__ fill, long fill_stride,
+                                    const void* __restrict__ fill_bias, int fb_dtype, int fill_cols, int n_rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int groups = cols >> 3, fill_groups = fill != nullptr ? fill_cols >> 3 : 0;
+    const int per_row = groups > fill_groups ? groups : fill_groups;
+    const long total = (long)n_rows * per_row;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / per_row), gq = (int)(i - (long)t * per_row);
+        const int j = gq << 3;
+        if (gq < groups) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(u + (size_t)t * u_stride + j);
+            const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            uint4 packed;
+            __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float2 v = __bfloat1622float2(in[k]);
+                if (bias) {
+                    v.x += load_as_f32(bias, b_dtype, j + 2 * k);
+                    v.y += load_as_f32(bias, b_dtype, j + 2 * k + 1);
+                }
+                out[k] = __floats2bfloat162_rn(gelu_tanh_fast(v.x), gelu_tanh_fast(v.y));
+            }
+            *reinterpret_cast<uint4*>(y + (size_t)t * y_stride + j) = packed;
+        }
+        if (gq < fill_groups) {
+            float4 a, b;
+            a.x = load_as_f32(fill_bias, fb_dtype, j), a.y = load_as_f32(fill_bias, fb_dtype, j + 1);
+            a.z = load_as_f32(fill_bias, fb_dtype, j + 2), a.w = load_as_f32(fill_bias, fb_dtype, j + 3);
+            b.x = load_as_f32(fill_bias, fb_dtype, j + 4), b.y = load_as_f32(fill_bias, fb_dtype, j + 5);
+            b.z = load_as_f32(fill_bias, fb_dtype, j + 6), b.w = load_as_f32(fill_bias, fb_dtype, j + 7);
+            float4* dst = reinterpret_cast<float4*>(fill + (size_t)t * fill_stride + j);
+            dst[0] = a;
+            dst[1] = b;
+        }
+    }
+}
+
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
 extern "C" int bfi_bias_act(const void* u, long u_stride, int dtype, const void* bias, int b_dtype, void* y, long y_stride,
                             int n_rows, int cols, float* fill, long fill_stride, const void* fill_bias, int fb_dtype,
                             int fill_cols, cudaStream_t stream) {
@@ -141,8 +224,18 @@ extern "C" int bfi_bias_act(const void* u, long u_stride, int dtype, const void*
     BFI_REQUIRE(fill == nullptr || (fill_bias != nullptr && fill_cols > 0 && fill_stride >= fill_cols),
                 "bias_act: the rows to fill need their bias and a stride of their width");
     if (n_rows == 0) return 0;
-    BFI_REQUIRE(n_rows <= 65535, "bias_act: %d rows are too many for one launch", n_rows);
     const int widest = (fill != nullptr && fill_cols > cols) ? fill_cols : cols;
+    if (dtype == BFI_BF16 && cols % 8 == 0 && u_stride % 8 == 0 && y_stride % 8 == 0 && aligned16(u) && aligned16(y) &&
+        (fill == nullptr || (fill_cols % 8 == 0 && fill_stride % 4 == 0 && aligned16(fill)))) {
+        const long total = (long)n_rows * (widest / 8);
+        long blocks = (total + 255) / 256;
+        const long most = (long)bfi_sm_count() * 16;
+        if (blocks > most) blocks = most;
+        bfi_launch(bias_act_vec_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (const bf16*)u, u_stride, bias, b_dtype, (bf16*)y,
+                   y_stride, cols, fill, fill_stride, fill_bias, fb_dtype, fill_cols, n_rows);
+        return bfi_check_launch("bias_act");
+    }
+    BFI_REQUIRE(n_rows <= 65535, "bias_act: %d rows are too many for one launch", n_rows);
     const dim3 grid((widest + 255) / 256, n_rows);
     if (dtype == BFI_F32)
         bfi_launch(bias_act_kernel<float>, grid, dim3(256), 0, stream, (const float*)u, u_stride, bias, b_dtype, (float*)y, y_stride,
@@ -165,12 +258,55 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ x, long x_stride, const T* _
     *p = from_f32<T>(to_f32(*p) * cw_sigmoid(to_f32(g[(size_t)t * g_stride + j / group])));
 }
 
+// bfloat16 rows in whole groups of 8 values that share a gate or have one each
+__global__ void sigmoid_gate_vec_kernel(bf16* __restrict__ x, long x_stride, const bf16* __restrict__ g, long g_stride, int cols,
+                                        int group, int n_rows) {
+    pdl_trigger();
+    pdl_wait();
+    const int per_row = cols >> 3;
+    const long total = (long)n_rows * per_row;
+    for (long i = (long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long)gridDim.x * blockDim.x) {
+        const int t = (int)(i / per_row), j = (int)(i - (long)t * per_row) << 3;
+        uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)t * x_stride + j);
+        __nv_bfloat162* v = reinterpret_cast<__nv_bfloat162*>(&raw);
+        float gate[8];
+        if (group == 1) {
+            const uint4 graw = *reinterpret_cast<const uint4*>(g + (size_t)t * g_stride + j);
+            const __nv_bfloat162* gv = reinterpret_cast<const __nv_bfloat162*>(&graw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(gv[k]);
+                gate[2 * k] = f.x, gate[2 * k + 1] = f.y;
+            }
+        } else {                                   // the 8 values lie in one group
+            const float one = __bfloat162float(g[(size_t)t * g_stride + j / group]);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) gate[k] = one;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(v[k]);
+            v[k] = __floats2bfloat162_rn(__fdividef(f.x, 1.0f + __expf(-gate[2 * k])), __fdividef(f.y, 1.0f + __expf(-gate[2 * k + 1])));
+        }
+        *reinterpret_cast<uint4*>(x + (size_t)t * x_stride + j) = raw;
+    }
+}
+
 extern "C" int bfi_sigmoid_gate(void* x, long x_stride, const void* g, long g_stride, int dtype, int n_rows, int cols, int group,
                                 cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(dtype), "sigmoid_gate: unknown dtype code %d", dtype);
     BFI_REQUIRE(n_rows >= 0 && cols > 0 && group > 0 && cols % group == 0 && x_stride >= cols && g_stride >= cols / group,
                 "sigmoid_gate: bad sizes rows=%d cols=%d group=%d", n_rows, cols, group);
     if (n_rows == 0) return 0;
+    if (dtype == BFI_BF16 && cols % 8 == 0 && x_stride % 8 == 0 && aligned16(x) && (group % 8 == 0 || (group == 1 && g_stride % 8 == 0 && aligned16(g)))) {
+        const long total = (long)n_rows * (cols / 8);
+        long blocks = (total + 255) / 256;
+        const long most = (long)bfi_sm_count() * 16;
+        if (blocks > most) blocks = most;
+        bfi_launch(sigmoid_gate_vec_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, (bf16*)x, x_stride, (const bf16*)g, g_stride, cols,
+                   group, n_rows);
+        return bfi_check_launch("sigmoid_gate");
+    }
     BFI_REQUIRE(n_rows <= 65535, "sigmoid_gate: %d rows are too many for one launch", n_rows);
     const dim3 grid((cols + 255) / 256, n_rows);
     if (dtype == BFI_F32)

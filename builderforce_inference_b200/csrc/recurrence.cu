@@ -596,6 +596,200 @@ __global__ void conv_forward_kernel(const TI* __restrict__ u, long u_stride, int
         for (int i = 0; i < taps - 1; ++i) st[(size_t)i * C] = in[taps - 2 - i];
 }
 
+// The same for bfloat16 outputs when channels, offsets and strides come in whole groups of 8: a thread owns 8
+// neighbouring channels of one token, reads every row it needs as 16 (or 32) bytes and writes 16.
+__device__ __forceinline__ void load8(const float* p, float (&v)[8]) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    v[0] = a.x, v[1] = a.y, v[2] = a.z, v[3] = a.w, v[4] = b.x, v[5] = b.y, v[6] = b.z, v[7] = b.w;
+}
+__device__ __forceinline__ void load8(const bf16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 f = __bfloat1622float2(h[k]);
+        v[2 * k] = f.x, v[2 * k + 1] = f.y;
+    }
+}
+__device__ __forceinline__ void store8(bf16* p, const float (&v)[8]) {
+    uint4 packed;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+    *reinterpret_cast<uint4*>(p) = packed;
+}
+
+template <typename TI>
+__global__ void conv_forward_vec_kernel(const TI* __restrict__ u, long u_stride, int u_off, const void* __restrict__ w,
+                                        const void* __restrict__ bias, int w_dtype, float* __restrict__ state,
+                                        bf16* __restrict__ y, long y_stride, const int* __restrict__ token_slot, int n_tokens,
+                                        int C, int taps, int fused_keep, const ConvExtras x) {
+    pdl_trigger();
+    pdl_wait();
+    const int groups = C >> 3;
+    const long total = (long)n_tokens * groups;
+    for (long idx = (long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long)gridDim.x * blockDim.x) {
+        const int t = (int)(idx / groups);
+        const int ch = (int)(idx - (long)t * groups) << 3;
+        const int slot = token_slot[t];
+        if (slot < 0) continue;
+        int own = 0;                               // rows before t that belong to the same sequence
+        while (own < taps - 1 && t - own - 1 >= 0 && token_slot[t - own - 1] == slot) ++own;
+        float* st = state + (size_t)slot * (taps - 1) * C + ch;
+        float acc[8], cur[8], in[8], prev[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = bias ? load_as_f32(bias, w_dtype, ch + k) : 0.0f;
+        for (int j = 0; j < taps; ++j) {
+            float* place = st + (size_t)(taps - 1 + own - j) * C;      // where the input j steps back is kept, if it is
+            if (j <= own)
+                load8(u + (size_t)(t - j) * u_stride + u_off + ch, in);
+            else
+                load8(place, in);
+            if (j == 0) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) cur[k] = in[k];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                acc[k] = fmaf(load_as_f32(w, w_dtype, (size_t)(ch + k) * taps + (taps - 1 - j)), in[k], acc[k]);
+            if (fused_keep) {
+                // one token per sequence (own is 0): the window moves on by one, so the input j - 1 steps back takes
+                // the place that has just been read
+                if (j >= 1) {
+                    reinterpret_cast<float4*>(place)[0] = make_float4(prev[0], prev[1], prev[2], prev[3]);
+                    reinterpret_cast<float4*>(place)[1] = make_float4(prev[4], prev[5], prev[6], prev[7]);
+                }
+#pragma unroll
+                for (int k = 0; k < 8; ++k) prev[k] = in[k];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (x.act) acc[k] = rec_silu(acc[k]);
+            if (x.add_input) acc[k] += cur[k];
+        }
+        if (ch >= x.mix_off) {
+            const size_t e = (size_t)t * x.mix_stride + (ch - x.mix_off);
+            if (x.mix_src != nullptr) {
+                const float lam = *x.mix_lambda;
+                float other[8];
+                load8(reinterpret_cast<const bf16*>(x.mix_src) + e, other);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = (1.0f - lam) * acc[k] + lam * other[k];
+            }
+            if (x.mix_dst != nullptr) store8(reinterpret_cast<bf16*>(x.mix_dst) + e, acc);
+        }
+        store8(y + (size_t)t * y_stride + ch, acc);
+        if (x.copy != nullptr) store8(reinterpret_cast<bf16*>(x.copy) + (size_t)t * x.copy_stride + ch, cur);
+    }
+}
+
+// The same again for 2 to 4 taps: a thread owns 8 neighbouring channels of CONV_TOK consecutive tokens, holds its
+// weights in registers and slides a window of the last TAPS inputs along the tokens, so a row is read once per
+// thread instead of once per tap.  The window is filled anew (from the rows before, then from the kept inputs)
+// where a thread's tokens begin and where the sequence changes.
+#define CONV_TOK 4
+
+template <typename TI, int TAPS>
+__global__ void __launch_bounds__(128)
+conv_forward_win_kernel(const TI* __restrict__ u, long u_stride, int u_off, const void* __restrict__ w,
+                        const void* __restrict__ bias, int w_dtype, float* __restrict__ state, bf16* __restrict__ y,
+                        long y_stride, const int* __restrict__ token_slot, int n_tokens, int C, int fused_keep,
+                        const ConvExtras x) {
+    pdl_trigger();
+    const int groups = C >> 3;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long tile = idx / groups;
+    const int ch = (int)(idx - tile * groups) << 3;
+    const bool live = tile * CONV_TOK < n_tokens;
+    float wt[TAPS][8], bs[8];                      // wt[j]: the weight of the input j steps back
+    if (live) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            bs[k] = bias ? load_as_f32(bias, w_dtype, ch + k) : 0.0f;
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) wt[j][k] = load_as_f32(w, w_dtype, (size_t)(ch + k) * TAPS + (TAPS - 1 - j));
+        }
+    }
+    pdl_wait();
+    if (!live) return;
+    float win[TAPS][8];                            // win[j]: the input j steps back from the current token
+    int prev_slot = -2;
+#pragma unroll
+    for (int i = 0; i < CONV_TOK; ++i) {
+        const int t = (int)tile * CONV_TOK + i;
+        if (t >= n_tokens) break;
+        const int slot = token_slot[t];
+        if (slot < 0) {
+            prev_slot = -2;
+            continue;
+        }
+        float* st = state + (size_t)slot * (TAPS - 1) * C + ch;
+        if (slot == prev_slot) {
+#pragma unroll
+            for (int j = TAPS - 1; j >= 1; --j) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) win[j][k] = win[j - 1][k];
+            }
+            load8(u + (size_t)t * u_stride + u_off + ch, win[0]);
+        } else {
+            int own = 0;                           // rows before t that belong to the same sequence
+            while (own < TAPS - 1 && t - own - 1 >= 0 && token_slot[t - own - 1] == slot) ++own;
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) {
+                if (j <= own)
+                    load8(u + (size_t)(t - j) * u_stride + u_off + ch, win[j]);
+                else
+                    load8(st + (size_t)(TAPS - 1 + own - j) * C, win[j]);
+            }
+        }
+        prev_slot = slot;
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = bs[k];
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = fmaf(wt[j][k], win[j][k], acc[k]);
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            if (x.act) acc[k] = rec_silu(acc[k]);
+            if (x.add_input) acc[k] += win[0][k];
+        }
+        if (ch >= x.mix_off) {
+            const size_t e = (size_t)t * x.mix_stride + (ch - x.mix_off);
+            if (x.mix_src != nullptr) {
+                const float lam = *x.mix_lambda;
+                float other[8];
+                load8(reinterpret_cast<const bf16*>(x.mix_src) + e, other);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = (1.0f - lam) * acc[k] + lam * other[k];
+            }
+            if (x.mix_dst != nullptr) store8(reinterpret_cast<bf16*>(x.mix_dst) + e, acc);
+        }
+        store8(y + (size_t)t * y_stride + ch, acc);
+        if (x.copy != nullptr) store8(reinterpret_cast<bf16*>(x.copy) + (size_t)t * x.copy_stride + ch, win[0]);
+        if (fused_keep) {                          // one token per sequence: the window moves on by one
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) {
+                float* dst = st + (size_t)(TAPS - 2 - j) * C;
+                reinterpret_cast<float4*>(dst)[0] = make_float4(win[j][0], win[j][1], win[j][2], win[j][3]);
+                reinterpret_cast<float4*>(dst)[1] = make_float4(win[j][4], win[j][5], win[j][6], win[j][7]);
+            }
+        }
+    }
+}
+
+template <typename TI, int TAPS>
+static void launch_conv_win(const void* u, long u_stride, int u_off, const void* w, const void* bias, int w_dtype, float* state,
+                            void* y, long y_stride, const int* token_slot, int n_tokens, int C, int fused, const ConvExtras& x,
+                            cudaStream_t stream) {
+    const long total = (long)((n_tokens + CONV_TOK - 1) / CONV_TOK) * (C / 8);
+    bfi_launch(conv_forward_win_kernel<TI, TAPS>, dim3((unsigned)((total + 127) / 128)), dim3(128), 0, stream, (const TI*)u, u_stride,
+               u_off, w, bias, w_dtype, state, (bf16*)y, y_stride, token_slot, n_tokens, C, fused, x);
+}
+
 template <typename T>
 __global__ void conv_keep_kernel(const T* __restrict__ u, long u_stride, int u_off, float* __restrict__ state,
                                  const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot, int C, int taps) {
@@ -637,6 +831,40 @@ extern "C" int bfi_causal_conv(const void* u, long u_stride, int u_off, int dtyp
     ConvExtras x;
     x.act = act, x.add_input = add_input, x.copy = copy, x.copy_stride = copy_stride;
     x.mix_off = mixes ? mix_off : C, x.mix_src = mix_src, x.mix_dst = mix_dst, x.mix_stride = mix_stride, x.mix_lambda = mix_lambda;
+    const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec = y_dtype == BFI_BF16 && C % 8 == 0 && u_off % 8 == 0 && u_stride % 8 == 0 && y_stride % 8 == 0 && al16(u) &&
+                     al16(y) && al16(state) && (copy == nullptr || (copy_stride % 8 == 0 && al16(copy))) &&
+                     (!mixes || (mix_off % 8 == 0 && mix_stride % 8 == 0 && (mix_src == nullptr || al16(mix_src)) &&
+                                 (mix_dst == nullptr || al16(mix_dst))));
+    if (vec && taps >= 2 && taps <= 4) {
+        const bool f32 = dtype == BFI_F32;
+#define BFI_CONV_WIN(TAPS)                                                                                                        \
+    if (f32)                                                                                                                      \
+        launch_conv_win<float, TAPS>(u, u_stride, u_off, w, bias, w_dtype, state, y, y_stride, token_slot, n_tokens, C, fused, x, \
+                                     stream);                                                                                     \
+    else                                                                                                                          \
+        launch_conv_win<bf16, TAPS>(u, u_stride, u_off, w, bias, w_dtype, state, y, y_stride, token_slot, n_tokens, C, fused, x,  \
+                                    stream)
+        if (taps == 2) {
+            BFI_CONV_WIN(2);
+        } else if (taps == 3) {
+            BFI_CONV_WIN(3);
+        } else {
+            BFI_CONV_WIN(4);
+        }
+#undef BFI_CONV_WIN
+    } else if (vec) {
+        const long total = (long)n_tokens * (C / 8);
+        long blocks = (total + threads - 1) / threads;
+        const long most = (long)bfi_sm_count() * 16;
+        if (blocks > most) blocks = most;
+        if (dtype == BFI_F32)
+            bfi_launch(conv_forward_vec_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const float*)u, u_stride, u_off,
+                       w, bias, w_dtype, state, (bf16*)y, y_stride, token_slot, n_tokens, C, taps, fused, x);
+        else
+            bfi_launch(conv_forward_vec_kernel<bf16>, dim3((unsigned)blocks), dim3(threads), 0, stream, (const bf16*)u, u_stride, u_off,
+                       w, bias, w_dtype, state, (bf16*)y, y_stride, token_slot, n_tokens, C, taps, fused, x);
+    } else
     if (dtype == BFI_F32 && y_dtype == BFI_F32)
         bfi_launch(conv_forward_kernel<float, float>, grid_t, dim3(threads), 0, stream, (const float*)u, u_stride, u_off, w, bias,
                    w_dtype, state, (float*)y, y_stride, token_slot, C, taps, fused, x);

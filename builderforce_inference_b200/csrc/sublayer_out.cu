@@ -70,6 +70,95 @@ __global__ void norm_add_kernel(float* __restrict__ x, long x_stride, const floa
         store_from_f32(h, h_dtype, (size_t)t * h_stride + j, xr[j] * scale2 * load_as_f32(w2, w2_dtype, j));
 }
 
+// The same for rows of a multiple of 4 values: a thread keeps its share of the gated row, and then of the new x, in
+// registers, so y, the gate's logits and x are read once.
+template <int VPT>
+__global__ void __launch_bounds__(256)
+norm_add_vec_kernel(float* __restrict__ x, long x_stride, const float* __restrict__ y, long y_stride, const void* __restrict__ w,
+                    int w_dtype, int width, float eps, float mult, const NormAddGate g, const void* __restrict__ w2, int w2_dtype,
+                    float eps2, void* __restrict__ h, int h_dtype, long h_stride) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[33];
+    const int t = blockIdx.x;
+    const int n4 = width >> 2;
+    const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * y_stride);
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)t * x_stride);
+    float4 v[VPT];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int j = i * 256 + threadIdx.x;
+        v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (j < n4) {
+            v[i] = yr[j];
+            if (g.logits != nullptr) {
+                const int c = j * 4;
+                float z[4];
+                if (g.dtype == BFI_F32) {
+                    const float4 q = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g.logits) + (size_t)t * g.stride + c);
+                    z[0] = q.x, z[1] = q.y, z[2] = q.z, z[3] = q.w;
+                } else {
+                    const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(g.logits) + (size_t)t * g.stride + c);
+                    const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&raw);
+                    const float2 a = __bfloat1622float2(hq[0]), b = __bfloat1622float2(hq[1]);
+                    z[0] = a.x, z[1] = a.y, z[2] = b.x, z[3] = b.y;
+                }
+                if (g.bias) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) z[k] += load_as_f32(g.bias, g.bias_dtype, c + k);
+                }
+                v[i].x *= out_sigmoid(z[0]);
+                v[i].y *= out_sigmoid(z[1]);
+                v[i].z *= out_sigmoid(z[2]);
+                v[i].w *= out_sigmoid(z[3]);
+            }
+            ss = fmaf(v[i].x, v[i].x, ss);
+            ss = fmaf(v[i].y, v[i].y, ss);
+            ss = fmaf(v[i].z, v[i].z, ss);
+            ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int j = i * 256 + threadIdx.x;
+        if (j >= n4) continue;
+        const int c = j * 4;
+        float4 o = xr[j];
+        o.x += mult * (v[i].x * scale * load_as_f32(w, w_dtype, c));
+        o.y += mult * (v[i].y * scale * load_as_f32(w, w_dtype, c + 1));
+        o.z += mult * (v[i].z * scale * load_as_f32(w, w_dtype, c + 2));
+        o.w += mult * (v[i].w * scale * load_as_f32(w, w_dtype, c + 3));
+        xr[j] = o;
+        v[i] = o;
+    }
+    if (h == nullptr) return;
+    float ss2 = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        if (i * 256 + threadIdx.x >= n4) continue;
+        ss2 = fmaf(v[i].x, v[i].x, ss2);
+        ss2 = fmaf(v[i].y, v[i].y, ss2);
+        ss2 = fmaf(v[i].z, v[i].z, ss2);
+        ss2 = fmaf(v[i].w, v[i].w, ss2);
+    }
+    ss2 = block_sum(ss2, scratch);
+    const float scale2 = 1.0f / sqrtf(ss2 / (float)width + eps2);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int j = i * 256 + threadIdx.x;
+        if (j >= n4) continue;
+        const int c = j * 4;
+        const size_t at = (size_t)t * h_stride + c;
+        store_from_f32(h, h_dtype, at, v[i].x * scale2 * load_as_f32(w2, w2_dtype, c));
+        store_from_f32(h, h_dtype, at + 1, v[i].y * scale2 * load_as_f32(w2, w2_dtype, c + 1));
+        store_from_f32(h, h_dtype, at + 2, v[i].z * scale2 * load_as_f32(w2, w2_dtype, c + 2));
+        store_from_f32(h, h_dtype, at + 3, v[i].w * scale2 * load_as_f32(w2, w2_dtype, c + 3));
+    }
+}
+
 extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stride, const void* w, int w_dtype,
                             int n_rows, int width, float eps, const void* w2, int w2_dtype, float eps2, void* h,
                             int h_dtype, long h_stride, float mult, const void* gate, int gate_dtype, long gate_stride,
@@ -85,6 +174,21 @@ extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stri
     NormAddGate g;
     g.logits = gate, g.dtype = gate_dtype, g.stride = gate_stride, g.bias = gate != nullptr ? gate_bias : nullptr;
     g.bias_dtype = gate_bias_dtype;
+    const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    // the plain normed add keeps the kernel (and with it the order of its sums) it has always had
+    if ((gate != nullptr || mult != 1.0f) && width % 4 == 0 && width <= 8 * 4 * 256 && x_stride % 4 == 0 && y_stride % 4 == 0 && al16(x) && al16(y) &&
+        (gate == nullptr || (gate_stride % 4 == 0 && (((uintptr_t)gate) & (gate_dtype == BFI_F32 ? 15 : 7)) == 0))) {
+        const int vpt = (width / 4 + 255) / 256;
+#define BFI_NORM_ADD(V)                                                                                                    \
+    bfi_launch(norm_add_vec_kernel<V>, dim3(n_rows), dim3(256), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, eps, \
+               mult, g, w2, w2_dtype, eps2, h, h_dtype, h_stride)
+        if (vpt <= 1) BFI_NORM_ADD(1);
+        else if (vpt == 2) BFI_NORM_ADD(2);
+        else if (vpt <= 4) BFI_NORM_ADD(4);
+        else BFI_NORM_ADD(8);
+#undef BFI_NORM_ADD
+        return bfi_check_launch("norm_add");
+    }
     bfi_launch(norm_add_kernel, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, eps, w2,
                w2_dtype, eps2, h, h_dtype, h_stride, mult, g);
     return bfi_check_launch("norm_add");

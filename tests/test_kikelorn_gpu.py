@@ -83,23 +83,25 @@ def packed(steps):
 # the convolution over time, its options and its per-sequence state
 # ------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("din,dout", [(F32, F32), (BF16, BF16), (F32, BF16)])
-@pytest.mark.parametrize("taps", [1, 2, 3, 5])
-def test_convolution_with_its_options_in_portions_and_single_tokens(din, dout, taps):
+@pytest.mark.parametrize("taps", [1, 2, 3, 4, 5])
+@pytest.mark.parametrize("C,off,mix_off", [(37, 3, 20), (40, 8, 24)])
+def test_convolution_with_its_options_in_portions_and_single_tokens(din, dout, taps, C, off, mix_off):
     """Three sequences in slots 4, 0 and 2 advance together through steps of unequal portions, down
     to single tokens; the output (the input plus its convolution), the copy of the input and the
-    mixing of the last channels are the plain ones over the whole sequences."""
+    mixing of the last channels are the plain ones over the whole sequences.  Channels and offsets
+    in whole groups of 8 take the kernels that move 16 bytes at a time (2 to 4 taps: the one that
+    slides a window along a thread's tokens)."""
     o = ops()
-    C, mix_off = 37, 20
     g = torch.Generator().manual_seed(taps)
     lens = {4: 31, 0: 9, 2: 17}
-    u = {s: torch.randn(n, C + 3, generator=g).to(din) for s, n in lens.items()}
+    u = {s: torch.randn(n, C + off, generator=g).to(din) for s, n in lens.items()}
     w = torch.randn(C, taps, generator=g).to(dout)
     src = {s: torch.randn(n, C - mix_off, generator=g).to(dout) for s, n in lens.items()}
     lam = torch.tensor([0.35], dtype=torch.float32, device=DEV)
     state = torch.zeros(6, taps - 1, C, dtype=torch.float32, device=DEV)
     ref = {}
     for s in lens:
-        uu = q64(u[s], din)[:, 3:]
+        uu = q64(u[s], din)[:, off:]
         y = uu + P.causal_conv(uu, q64(w, dout))
         y[:, mix_off:] = (1.0 - 0.35) * y[:, mix_off:] + 0.35 * q64(src[s], dout)
         ref[s] = y
@@ -113,12 +115,12 @@ def test_convolution_with_its_options_in_portions_and_single_tokens(din, dout, t
         cp = torch.empty_like(y)
         dst = torch.empty(rows.shape[0], C - mix_off, dtype=dout, device=DEV)
         single = all(n == 1 for _, n in step)
-        o.causal_conv(rows, 3, C, w.to(DEV), None, state, y, slot_of, cu, slots, len(step), single_tokens=single,
+        o.causal_conv(rows, off, C, w.to(DEV), None, state, y, slot_of, cu, slots, len(step), single_tokens=single,
                       act=o.CONV_ACT_NONE, add_input=True, copy=cp, mix_off=mix_off, mix_src=mixes, mix_dst=dst, mix_lambda=lam)
         want = torch.cat([ref[s][at[s]:at[s] + n] for s, n in step])
         assert rel_err(y, want) < (1e-5 if dout == F32 else 1e-2), (taps, step)
         assert torch.equal(dst, y[:, mix_off:])
-        assert torch.equal(cp.cpu(), rows[:, 3:].to(dout).cpu())
+        assert torch.equal(cp.cpu(), rows[:, off:].to(dout).cpu())
         for s, n in step:
             at[s] += n
 
