@@ -495,7 +495,9 @@ def kernel_run(a) -> int:
     recurrence with a step size per head over prompts / over single tokens), ``--kernel attention_latent --seqs N --rows T --ctx C
     --heads H`` (the latent attention; --rows 1: single tokens behind C cached ones), ``--kernel weight_stream --shape S [--stages R] [--ksplit Z]`` (the
     matrix read once through the few-row products' TMA rings and nothing else: the floor under
-    them).  Weights rotate over enough copies to exceed L2.  Prints one JSON line."""
+    them), ``--kernel causal_conv|gated_scan|norm_add_gated|bias_gelu --seqs N --rows T --width W`` (what stands in front
+    of and behind an out-norm block's sublayers, the minGRU's recurrence, the dense feed-forward's bias and GELU).
+    Weights rotate over enough copies to exceed L2.  Prints one JSON line."""
     import torch
     from builderforce_inference_b200.kernels import fast_ops
     dev = torch.device("cuda:0")
@@ -557,6 +559,56 @@ def kernel_run(a) -> int:
         # per token and head: scores and their use within a chunk (causal half of 64 x 64), q S and the state update
         flops = n_seq * t_new * h * (2.0 * d * d * 2 + (2.0 * 32 * (d + d) if chunks else 0.0))
         what = {"seqs": n_seq, "new_tokens": t_new, "heads": h, "dim": d, "vdim": d}
+    elif a.kernel in ("causal_conv", "gated_scan", "norm_add_gated", "bias_gelu"):
+        # the kernels around an out-norm block's sublayers and of the minGRU: --seqs prompts of --rows tokens, --width channels
+        from builderforce_inference_b200.kernels import ops
+        n_seq, t_new, w = a.seqs, a.rows, a.width
+        n = n_seq * t_new
+        copies = max(2, int(600e6 // (n * w * 12)) + 1)
+        cu = torch.arange(0, (n_seq + 1) * t_new, t_new, dtype=torch.int32, device=dev)
+        slots = torch.arange(n_seq, dtype=torch.int32, device=dev)
+        slot_of = slots.repeat_interleave(t_new)
+        bf, single = torch.bfloat16, t_new == 1
+        if a.kernel == "causal_conv":       # x + conv(x) off the float32 stream, with the plain copy: what stands in front of a sublayer
+            taps = KIKELORN_TAPS
+            xs = [torch.randn(n, w, device=dev) for _ in range(copies)]
+            cw = torch.randn(w, taps, device=dev, dtype=bf) * 0.3
+            state = torch.zeros(n_seq, taps - 1, w, device=dev)
+            h, plain = torch.empty(n, w, device=dev, dtype=bf), torch.empty(n, w, device=dev, dtype=bf)
+
+            def one(i):
+                ops.causal_conv(xs[i % copies], 0, w, cw, None, state, h, slot_of, cu, slots, n_seq, single_tokens=single,
+                                act=ops.CONV_ACT_NONE, add_input=True, copy=plain)
+            bytes_moved = n * w * (4 + 2 + 2)
+        elif a.kernel == "gated_scan":      # the minGRU's recurrence over [z | u | g] with its output gate
+            projs = [torch.randn(n, 3 * w, device=dev, dtype=bf) for _ in range(copies)]
+            bz, bu = torch.randn(w, device=dev), torch.randn(w, device=dev)
+            state = torch.zeros(n_seq, w, device=dev)
+            y = torch.empty(n, w, device=dev, dtype=bf)
+
+            def one(i):
+                ops.gated_scan(projs[i % copies], 0, w, 2 * w, w, bz, bu, y, state, cu, slots, n_seq, t_new)
+            bytes_moved = n * w * 2 * 4
+        elif a.kernel == "norm_add_gated":  # x += mult * norm(y * sigmoid(g + b)): what stands behind a sublayer
+            ys = [torch.randn(n, w, device=dev) for _ in range(copies)]
+            x = torch.zeros(n, w, device=dev)
+            gl = torch.randn(n, w, device=dev, dtype=bf)
+            gb, nw = torch.randn(w, device=dev, dtype=bf), torch.ones(w, device=dev, dtype=bf)
+
+            def one(i):
+                ops.norm_add(x, ys[i % copies], nw, 1e-6, mult=0.7, gate=gl, gate_bias=gb)
+            bytes_moved = n * w * (4 + 2 + 4 + 4)
+        else:                               # gelu_tanh(u + b) in place, and the next product's bias into its float32 target rows
+            ff = 3 * w
+            us_ = [torch.randn(n, ff, device=dev, dtype=bf) for _ in range(copies)]
+            b1, b2 = torch.randn(ff, device=dev, dtype=bf), torch.randn(w, device=dev, dtype=bf)
+            fill = torch.empty(n, w, device=dev)
+
+            def one(i):
+                ops.bias_act(us_[i % copies], b1, us_[i % copies], fill=fill, fill_bias=b2)
+            bytes_moved = n * (ff * 4 + w * 4)
+        flops = 0.0
+        what = {"seqs": n_seq, "new_tokens": t_new, "width": w}
     elif a.kernel in ("decay_scan", "decay_step"):
         # the recurrence with a step size per head (state-space form): --seqs prompts of --rows tokens (chunked from 192
         # tokens on), or --rows sequences of one token
@@ -848,8 +900,10 @@ def main() -> int:
     ap.add_argument("--seqs", type=int, default=1, help="kernel mode, prompt attention: prompts of --rows tokens each")
     ap.add_argument("--kernel", default=None, choices=["skinny_gemm", "gemm_tcgen05", "weight_stream", "qk_norm_rope", "attention_decode",
                                                        "attention_prefill", "attention_prefill_tcgen05", "lightning_chunks", "lightning_scan",
-                                                       "qk_prepare", "decay_scan", "decay_step", "attention_latent"],
+                                                       "qk_prepare", "decay_scan", "decay_step", "attention_latent", "causal_conv",
+                                                       "gated_scan", "norm_add_gated", "bias_gelu"],
                     help="time one kernel instead of the model (see kernel_run)")
+    ap.add_argument("--width", type=int, default=2048, help="kernel mode, the channel-wise kernels: channels of a row")
     ap.add_argument("--shape", default="qkv", choices=sorted(KERNEL_SHAPES))
     ap.add_argument("--eager", action="store_true", help="with --kernel: plain launches instead of one CUDA graph")
     ap.add_argument("--stages", type=int, default=6, help="--kernel weight_stream: 16 KB tiles in a block's ring (1..12)")

@@ -179,6 +179,7 @@ __global__ void bias_act_vec_kernel(const bf16* __restrict__ u, long u_stride, c
                                     const void* __restrict__ fill_bias, int fb_dtype, int fill_cols, int n_rows) {
     pdl_trigger();
     pdl_wait();
+    const bool bias_vec = b_dtype == BFI_BF16 && (reinterpret_cast<uintptr_t>(bias) & 15) == 0;
     const int groups = cols >> 3, fill_groups = fill != nullptr ? fill_cols >> 3 : 0;
     const int per_row = groups > fill_groups ? groups : fill_groups;
     const long total = (long)n_rows * per_row;
@@ -190,13 +191,24 @@ __global__ void bias_act_vec_kernel(const bf16* __restrict__ u, long u_stride, c
             const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
             uint4 packed;
             __nv_bfloat162* out = reinterpret_cast<__nv_bfloat162*>(&packed);
+            float b8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            if (bias && bias_vec) {                // 16 bytes of a bfloat16 bias at once
+                const uint4 braw = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(bias) + j);
+                const __nv_bfloat162* bh = reinterpret_cast<const __nv_bfloat162*>(&braw);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const float2 f = __bfloat1622float2(bh[k]);
+                    b8[2 * k] = f.x, b8[2 * k + 1] = f.y;
+                }
+            } else if (bias) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) b8[k] = load_as_f32(bias, b_dtype, j + k);
+            }
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 float2 v = __bfloat1622float2(in[k]);
-                if (bias) {
-                    v.x += load_as_f32(bias, b_dtype, j + 2 * k);
-                    v.y += load_as_f32(bias, b_dtype, j + 2 * k + 1);
-                }
+                v.x += b8[2 * k];
+                v.y += b8[2 * k + 1];
                 out[k] = __floats2bfloat162_rn(gelu_tanh_fast(v.x), gelu_tanh_fast(v.y));
             }
             *reinterpret_cast<uint4*>(y + (size_t)t * y_stride + j) = packed;

@@ -685,9 +685,9 @@ __global__ void conv_forward_vec_kernel(const TI* __restrict__ u, long u_stride,
 }
 
 // The same again for 2 to 4 taps: a thread owns 8 neighbouring channels of CONV_TOK consecutive tokens, holds its
-// weights in registers and slides a window of the last TAPS inputs along the tokens, so a row is read once per
-// thread instead of once per tap.  The window is filled anew (from the rows before, then from the kept inputs)
-// where a thread's tokens begin and where the sequence changes.
+// weights in registers and reads its tokens' rows and the TAPS - 1 rows before them once, all loads in flight
+// together, so a row is read once per thread instead of once per tap; a tap that reaches back past the rows of
+// the token's own sequence reads the kept inputs instead.
 #define CONV_TOK 4
 
 template <typename TI, int TAPS>
@@ -704,58 +704,91 @@ conv_forward_win_kernel(const TI* __restrict__ u, long u_stride, int u_off, cons
     const bool live = tile * CONV_TOK < n_tokens;
     float wt[TAPS][8], bs[8];                      // wt[j]: the weight of the input j steps back
     if (live) {
+        // the 8 channels' taps lie side by side in the weights: 8 * TAPS values, read 16 bytes at a time
+        float flat[8 * TAPS];
+        if (w_dtype == BFI_BF16) {
+            const bf16* p = reinterpret_cast<const bf16*>(w) + (size_t)ch * TAPS;
+#pragma unroll
+            for (int q = 0; q < TAPS; ++q) {
+                float part[8];
+                load8(p + 8 * q, part);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) flat[8 * q + k] = part[k];
+            }
+        } else {
+            const float* p = reinterpret_cast<const float*>(w) + (size_t)ch * TAPS;
+#pragma unroll
+            for (int q = 0; q < TAPS; ++q) {
+                float part[8];
+                load8(p + 8 * q, part);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) flat[8 * q + k] = part[k];
+            }
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             bs[k] = bias ? load_as_f32(bias, w_dtype, ch + k) : 0.0f;
 #pragma unroll
-            for (int j = 0; j < TAPS; ++j) wt[j][k] = load_as_f32(w, w_dtype, (size_t)(ch + k) * TAPS + (TAPS - 1 - j));
+            for (int j = 0; j < TAPS; ++j) wt[j][k] = flat[k * TAPS + (TAPS - 1 - j)];
         }
     }
     pdl_wait();
     if (!live) return;
-    float win[TAPS][8];                            // win[j]: the input j steps back from the current token
-    int prev_slot = -2;
+    // the slots of the tile's rows and of the TAPS - 1 rows before them, then all those rows at once: no load
+    // waits for another
+    constexpr int ROWS = CONV_TOK + TAPS - 1;
+    const int t0 = (int)tile * CONV_TOK;
+    int sl[ROWS];
+    float rows[ROWS][8];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const int tt = t0 - (TAPS - 1) + r;
+        sl[r] = (tt >= 0 && tt < n_tokens) ? token_slot[tt] : -1;
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+        const int tt = t0 - (TAPS - 1) + r;
+        if (sl[r] >= 0) load8(u + (size_t)tt * u_stride + u_off + ch, rows[r]);
+    }
 #pragma unroll
     for (int i = 0; i < CONV_TOK; ++i) {
-        const int t = (int)tile * CONV_TOK + i;
-        if (t >= n_tokens) break;
-        const int slot = token_slot[t];
-        if (slot < 0) {
-            prev_slot = -2;
-            continue;
-        }
+        const int ri = i + TAPS - 1;
+        const int t = t0 + i;
+        const int slot = sl[ri];
+        if (slot < 0) continue;                    // padding, or past the step's tokens
         float* st = state + (size_t)slot * (TAPS - 1) * C + ch;
-        if (slot == prev_slot) {
+        int own = 0;                               // rows before t that belong to the same sequence
 #pragma unroll
-            for (int j = TAPS - 1; j >= 1; --j) {
-#pragma unroll
-                for (int k = 0; k < 8; ++k) win[j][k] = win[j - 1][k];
-            }
-            load8(u + (size_t)t * u_stride + u_off + ch, win[0]);
-        } else {
-            int own = 0;                           // rows before t that belong to the same sequence
-            while (own < TAPS - 1 && t - own - 1 >= 0 && token_slot[t - own - 1] == slot) ++own;
-#pragma unroll
-            for (int j = 0; j < TAPS; ++j) {
-                if (j <= own)
-                    load8(u + (size_t)(t - j) * u_stride + u_off + ch, win[j]);
-                else
-                    load8(st + (size_t)(TAPS - 1 + own - j) * C, win[j]);
-            }
-        }
-        prev_slot = slot;
-        float acc[8];
+        for (int j = 1; j < TAPS; ++j)
+            if (own == j - 1 && sl[ri - j] == slot) own = j;
+        float acc[8], kept[TAPS][8];               // kept[j]: the input j steps back, where it comes from the state
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[k] = bs[k];
 #pragma unroll
         for (int j = 0; j < TAPS; ++j) {
+            if (j <= own) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = fmaf(wt[j][k], win[j][k], acc[k]);
+                for (int k = 0; k < 8; ++k) acc[k] = fmaf(wt[j][k], rows[ri - j][k], acc[k]);
+            } else {
+                load8(st + (size_t)(TAPS - 1 + own - j) * C, kept[j]);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = fmaf(wt[j][k], kept[j][k], acc[k]);
+            }
+        }
+        if (fused_keep) {
+            // one token per sequence: the window moves on by one, after every place of it has been read
+#pragma unroll
+            for (int j = 0; j < TAPS - 1; ++j) {
+                float* dst = st + (size_t)(TAPS - 2 - j) * C;
+                const float* src = j <= own ? rows[ri - j] : kept[j];
+                reinterpret_cast<float4*>(dst)[0] = make_float4(src[0], src[1], src[2], src[3]);
+                reinterpret_cast<float4*>(dst)[1] = make_float4(src[4], src[5], src[6], src[7]);
+            }
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
             if (x.act) acc[k] = rec_silu(acc[k]);
-            if (x.add_input) acc[k] += win[0][k];
+            if (x.add_input) acc[k] += rows[ri][k];
         }
         if (ch >= x.mix_off) {
             const size_t e = (size_t)t * x.mix_stride + (ch - x.mix_off);
@@ -769,15 +802,7 @@ conv_forward_win_kernel(const TI* __restrict__ u, long u_stride, int u_off, cons
             if (x.mix_dst != nullptr) store8(reinterpret_cast<bf16*>(x.mix_dst) + e, acc);
         }
         store8(y + (size_t)t * y_stride + ch, acc);
-        if (x.copy != nullptr) store8(reinterpret_cast<bf16*>(x.copy) + (size_t)t * x.copy_stride + ch, win[0]);
-        if (fused_keep) {                          // one token per sequence: the window moves on by one
-#pragma unroll
-            for (int j = 0; j < TAPS - 1; ++j) {
-                float* dst = st + (size_t)(TAPS - 2 - j) * C;
-                reinterpret_cast<float4*>(dst)[0] = make_float4(win[j][0], win[j][1], win[j][2], win[j][3]);
-                reinterpret_cast<float4*>(dst)[1] = make_float4(win[j][4], win[j][5], win[j][6], win[j][7]);
-            }
-        }
+        if (x.copy != nullptr) store8(reinterpret_cast<bf16*>(x.copy) + (size_t)t * x.copy_stride + ch, rows[ri]);
     }
 }
 
@@ -836,7 +861,7 @@ extern "C" int bfi_causal_conv(const void* u, long u_stride, int u_off, int dtyp
                      al16(y) && al16(state) && (copy == nullptr || (copy_stride % 8 == 0 && al16(copy))) &&
                      (!mixes || (mix_off % 8 == 0 && mix_stride % 8 == 0 && (mix_src == nullptr || al16(mix_src)) &&
                                  (mix_dst == nullptr || al16(mix_dst))));
-    if (vec && taps >= 2 && taps <= 4) {
+    if (vec && taps >= 2 && taps <= 4 && al16(w)) {
         const bool f32 = dtype == BFI_F32;
 #define BFI_CONV_WIN(TAPS)                                                                                                        \
     if (f32)                                                                                                                      \
