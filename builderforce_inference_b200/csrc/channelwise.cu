@@ -31,7 +31,7 @@ __device__ __forceinline__ float cw_sigmoid(float x) {
 struct ScanArgs {
     long p_stride, y_stride;
     int z_off, u_off, g_off;        // g_off < 0: no output gate
-    int C, cand;
+    int C, cand, tiles;
     const float *z_bias, *u_bias;   // float32 [C] or null
     const int *cu_seqlens, *seq_slot;
 };
@@ -61,8 +61,10 @@ gated_scan_kernel(const T* __restrict__ proj, T* __restrict__ y, float* __restri
     pdl_trigger();
     __shared__ float seg_a[SCAN_MAX_WARPS][32], seg_b[SCAN_MAX_WARPS][32];
     const int seq = blockIdx.x;
-    const int lane = threadIdx.x, w = threadIdx.y, n_w = blockDim.y;
-    const int ch = blockIdx.y * 32 + lane;
+    // a.tiles > 1 (steps whose sequences bring few tokens): the block's warps are channel tiles of one segment each
+    const int lane = threadIdx.x;
+    const int w = a.tiles > 1 ? 0 : threadIdx.y, n_w = a.tiles > 1 ? 1 : blockDim.y;
+    const int ch = (a.tiles > 1 ? blockIdx.y * a.tiles + threadIdx.y : blockIdx.y) * 32 + lane;
     const bool live = ch < a.C;
     const float bz = (live && a.z_bias) ? a.z_bias[ch] : 0.0f;
     const float bu = (live && a.u_bias) ? a.u_bias[ch] : 0.0f;
@@ -94,9 +96,11 @@ gated_scan_kernel(const T* __restrict__ proj, T* __restrict__ y, float* __restri
             }
         }
     }
-    seg_a[w][lane] = A;
-    seg_b[w][lane] = B;
-    __syncthreads();
+    if (n_w > 1) {
+        seg_a[w][lane] = A;
+        seg_b[w][lane] = B;
+        __syncthreads();
+    }
     if (!live) return;
     float S = state[(size_t)slot * a.C + ch];
     for (int i = 0; i < w; ++i) S = fmaf(seg_a[i][lane], S, seg_b[i][lane]);
@@ -136,10 +140,11 @@ extern "C" int bfi_gated_scan(const void* proj, long p_stride, int z_off, int u_
     int warps = (max_seq_tokens + 15) / 16;        // segments of at least 16 tokens, as many as a block has warps
     if (warps < 1) warps = 1;
     if (warps > SCAN_MAX_WARPS) warps = SCAN_MAX_WARPS;
-    const dim3 grid(n_seqs, (C + 31) / 32), block(32, warps);
+    const int tiles = warps == 1 ? 4 : 1;          // one segment: four channel tiles share a block
+    const dim3 grid(n_seqs, ((C + 31) / 32 + tiles - 1) / tiles), block(32, warps == 1 ? tiles : warps);
     BFI_REQUIRE(grid.y <= 65535, "gated_scan: %d channels are too many for one launch", C);
     ScanArgs a;
-    a.p_stride = p_stride, a.y_stride = y_stride, a.z_off = z_off, a.u_off = u_off, a.g_off = g_off, a.C = C, a.cand = cand;
+    a.p_stride = p_stride, a.y_stride = y_stride, a.z_off = z_off, a.u_off = u_off, a.g_off = g_off, a.C = C, a.cand = cand, a.tiles = tiles;
     a.z_bias = z_bias, a.u_bias = u_bias, a.cu_seqlens = cu_seqlens, a.seq_slot = seq_slot;
     if (dtype == BFI_F32)
         bfi_launch(gated_scan_kernel<float>, grid, block, 0, stream, (const float*)proj, (float*)y, state, a);

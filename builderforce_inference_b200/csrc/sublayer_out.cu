@@ -72,52 +72,68 @@ __global__ void norm_add_kernel(float* __restrict__ x, long x_stride, const floa
 
 // The same for rows of a multiple of 4 values: a thread keeps its share of the gated row, and then of the new x, in
 // registers, so y, the gate's logits and x are read once.
-template <int VPT>
+__device__ __forceinline__ float4 load4_as_f32(const void* p, int dtype, size_t i) {      // i a multiple of 4, p aligned for it
+    if (dtype == BFI_F32) return *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p) + i);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
+// EARLY (few rows: a single-token step): the weights before the wait for the kernel before this one, and x asked for
+// together with y and the gate's logits, so the row costs one trip to memory instead of two; with many rows the
+// registers that takes cost more in resident rows than the trip does.
+template <int VPT, bool EARLY>
 __global__ void __launch_bounds__(256)
 norm_add_vec_kernel(float* __restrict__ x, long x_stride, const float* __restrict__ y, long y_stride, const void* __restrict__ w,
                     int w_dtype, int width, float eps, float mult, const NormAddGate g, const void* __restrict__ w2, int w2_dtype,
                     float eps2, void* __restrict__ h, int h_dtype, long h_stride) {
     pdl_trigger();
-    pdl_wait();
     __shared__ float scratch[33];
     const int t = blockIdx.x;
     const int n4 = width >> 2;
+    // the weights and the gate's bias do not come from the kernel before this one: fetched before the wait
+    float4 wv[EARLY ? VPT : 1];
+    if (EARLY) {
+#pragma unroll
+        for (int i = 0; i < VPT; ++i) {
+            const int j = i * 256 + threadIdx.x;
+            wv[i] = j < n4 ? load4_as_f32(w, w_dtype, (size_t)j * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    pdl_wait();
     const float4* yr = reinterpret_cast<const float4*>(y + (size_t)t * y_stride);
     float4* xr = reinterpret_cast<float4*>(x + (size_t)t * x_stride);
-    float4 v[VPT];
-    float ss = 0.0f;
+    float4 v[VPT], xv[EARLY ? VPT : 1];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int j = i * 256 + threadIdx.x;
         v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (j < n4) {
             v[i] = yr[j];
-            if (g.logits != nullptr) {
-                const int c = j * 4;
-                float z[4];
-                if (g.dtype == BFI_F32) {
-                    const float4 q = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(g.logits) + (size_t)t * g.stride + c);
-                    z[0] = q.x, z[1] = q.y, z[2] = q.z, z[3] = q.w;
-                } else {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(g.logits) + (size_t)t * g.stride + c);
-                    const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&raw);
-                    const float2 a = __bfloat1622float2(hq[0]), b = __bfloat1622float2(hq[1]);
-                    z[0] = a.x, z[1] = a.y, z[2] = b.x, z[3] = b.y;
-                }
-                if (g.bias) {
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) z[k] += load_as_f32(g.bias, g.bias_dtype, c + k);
-                }
-                v[i].x *= out_sigmoid(z[0]);
-                v[i].y *= out_sigmoid(z[1]);
-                v[i].z *= out_sigmoid(z[2]);
-                v[i].w *= out_sigmoid(z[3]);
-            }
-            ss = fmaf(v[i].x, v[i].x, ss);
-            ss = fmaf(v[i].y, v[i].y, ss);
-            ss = fmaf(v[i].z, v[i].z, ss);
-            ss = fmaf(v[i].w, v[i].w, ss);
+            if (EARLY) xv[i] = xr[j];
         }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int j = i * 256 + threadIdx.x;
+        if (j >= n4) continue;
+        if (g.logits != nullptr) {
+            float4 z = load4_as_f32(g.logits, g.dtype, (size_t)t * g.stride + (size_t)j * 4);
+            if (g.bias != nullptr) {
+                const float4 b = load4_as_f32(g.bias, g.bias_dtype, (size_t)j * 4);
+                z.x += b.x, z.y += b.y, z.z += b.z, z.w += b.w;
+            }
+            v[i].x *= out_sigmoid(z.x);
+            v[i].y *= out_sigmoid(z.y);
+            v[i].z *= out_sigmoid(z.z);
+            v[i].w *= out_sigmoid(z.w);
+        }
+        ss = fmaf(v[i].x, v[i].x, ss);
+        ss = fmaf(v[i].y, v[i].y, ss);
+        ss = fmaf(v[i].z, v[i].z, ss);
+        ss = fmaf(v[i].w, v[i].w, ss);
     }
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)width + eps);
@@ -125,12 +141,12 @@ norm_add_vec_kernel(float* __restrict__ x, long x_stride, const float* __restric
     for (int i = 0; i < VPT; ++i) {
         const int j = i * 256 + threadIdx.x;
         if (j >= n4) continue;
-        const int c = j * 4;
-        float4 o = xr[j];
-        o.x += mult * (v[i].x * scale * load_as_f32(w, w_dtype, c));
-        o.y += mult * (v[i].y * scale * load_as_f32(w, w_dtype, c + 1));
-        o.z += mult * (v[i].z * scale * load_as_f32(w, w_dtype, c + 2));
-        o.w += mult * (v[i].w * scale * load_as_f32(w, w_dtype, c + 3));
+        float4 o = EARLY ? xv[i] : xr[j];
+        const float4 ww = EARLY ? wv[i] : load4_as_f32(w, w_dtype, (size_t)j * 4);
+        o.x += mult * (v[i].x * scale * ww.x);
+        o.y += mult * (v[i].y * scale * ww.y);
+        o.z += mult * (v[i].z * scale * ww.z);
+        o.w += mult * (v[i].w * scale * ww.w);
         xr[j] = o;
         v[i] = o;
     }
@@ -176,12 +192,21 @@ extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stri
     g.bias_dtype = gate_bias_dtype;
     const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     // the plain normed add keeps the kernel (and with it the order of its sums) it has always had
-    if ((gate != nullptr || mult != 1.0f) && width % 4 == 0 && width <= 8 * 4 * 256 && x_stride % 4 == 0 && y_stride % 4 == 0 && al16(x) && al16(y) &&
+    const auto al_for = [](const void* p, int dt) { return (reinterpret_cast<uintptr_t>(p) & (dt == BFI_F32 ? 15 : 7)) == 0; };
+    if ((gate != nullptr || mult != 1.0f) && al_for(w, w_dtype) && (gate_bias == nullptr || al_for(gate_bias, gate_bias_dtype)) && width % 4 == 0 &&
+        width <= 8 * 4 * 256 && x_stride % 4 == 0 && y_stride % 4 == 0 && al16(x) && al16(y) &&
         (gate == nullptr || (gate_stride % 4 == 0 && (((uintptr_t)gate) & (gate_dtype == BFI_F32 ? 15 : 7)) == 0))) {
         const int vpt = (width / 4 + 255) / 256;
+        const bool early = n_rows <= 2 * bfi_sm_count();
 #define BFI_NORM_ADD(V)                                                                                                    \
-    bfi_launch(norm_add_vec_kernel<V>, dim3(n_rows), dim3(256), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, eps, \
-               mult, g, w2, w2_dtype, eps2, h, h_dtype, h_stride)
+    do {                                                                                                                     \
+    if (early)                                                                                                               \
+        bfi_launch(norm_add_vec_kernel<V, true>, dim3(n_rows), dim3(256), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, \
+                   eps, mult, g, w2, w2_dtype, eps2, h, h_dtype, h_stride);                                                  \
+    else                                                                                                                     \
+        bfi_launch(norm_add_vec_kernel<V, false>, dim3(n_rows), dim3(256), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, \
+                   eps, mult, g, w2, w2_dtype, eps2, h, h_dtype, h_stride);                                                  \
+    } while (0)
         if (vpt <= 1) BFI_NORM_ADD(1);
         else if (vpt == 2) BFI_NORM_ADD(2);
         else if (vpt <= 4) BFI_NORM_ADD(4);
