@@ -399,7 +399,7 @@ def kikelorn_config(width, heads, kv, d, ff, layers):
     gru = {"width": 3 * width // 2}
     kinds = [("attention", att), ("latent_attention", lat), ("mingru", gru), ("attention", att)]
     return {"architecture": "Kikelorn", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
-            "residual_mult": 0.7, "canon": {"taps": KIKELORN_TAPS},
+            "residual_mult": 0.5, "canon": {"taps": KIKELORN_TAPS},
             "layers": [{"type": kinds[i % 4][0], "mixer": kinds[i % 4][1], "mlp": {"kind": "dense", "ff": ff}} for i in range(layers)]}
 
 

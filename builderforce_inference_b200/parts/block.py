@@ -186,7 +186,6 @@ class OutNormBlock(Block):
 
     def _input(self, ctx, x, i: int, kept):
         """What sublayer ``i`` reads (convolved) and what its gate reads (plain), in the activation dtype."""
-        import torch
         h = ctx.rows("block.in", self.width)
         plain = ctx.rows("block.plain", self.width) if self.has_gate else None
         if self.taps is None:

@@ -200,8 +200,8 @@ def random_config(seed):
             rd = rng.choice([0, 2, 8, 16, 32])
             r = None
             if rd and rng.random() < 0.9:
-                sc = (rng.choice([2.0, 4.0]), rng.choice([32, 512]), rng.choice([16.0, 32.0]), 1.0) if rng.random() < 0.6 else None
-                r = rot(rng.choice([1e3, 2.5e5]), rd, sc)
+                sc = (rng.choice([2.0, 8.0]), rng.choice([32, 1024]), rng.choice([16.0, 24.0]), 1.0) if rng.random() < 0.6 else None
+                r = rot(rng.choice([1e3, 3e5]), rd, sc)
             d = rng.choice([4, 8, 16, 32])
             lay = lat(rng.choice([1, 2, 3, 4, 8]), d, rd, rng.choice([4, 8, 16, 32, 40]), rng.choice([2, 8, 16, 24, 64, 128]),
                       rng.choice([1, 6, 16, 48]), rng.choice([0.1, (d + rd) ** -0.5, 0.3]), r)

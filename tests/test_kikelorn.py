@@ -136,7 +136,7 @@ def test_reordered_rows_turn_adjacent_pairs_as_halves():
     assert torch.allclose(turned[..., perm], P.rotate(v[..., perm], cos, sin, dims, "half"))
 
 
-@pytest.mark.parametrize("base,dims,scaling", [(250000.0, 16, (4.0, 512, 32.0, 1.0)), (1e4, 8, None), (100.0, 6, (3.0, 64, 16.0, 2.0)),
+@pytest.mark.parametrize("base,dims,scaling", [(3.0e5, 12, (8.0, 256, 16.0, 1.0)), (1e4, 8, None), (100.0, 6, (3.0, 64, 16.0, 2.0)),
                                                (5e3, 2, (2.0, 32, 8.0, 1.0))])
 def test_rotation_table_is_the_plain_one(base, dims, scaling):
     sc = dict(zip(("factor", "original", "fast", "slow"), scaling)) if scaling else None

@@ -3,7 +3,6 @@ every mechanism's kernels alone, then whole models with sizes of their own, step
 token, in portions, in unequal batches, over reused slots and pages, and generated from greedily.
 
 Some tests shape their inputs so that one far token, a chunk's edge or a gate decides the result."""
-import copy
 import json
 import os
 
@@ -353,7 +352,7 @@ def test_a_token_just_inside_and_just_outside_the_chunk(chunk, decoded):
     chunk's first position on.  Changing the third token before the chunk changes nothing at the
     chunk's last position; changing the chunk's first token does.  In a prompt, and with the last
     chunk decoded token by token (its first token then arrives alone, pages and chunk edges apart)."""
-    cfg = config(97, 32, 1e-5, 2.0, 0.7, 2, [with_mlp(att(4, 2, 8, 12, 2, 0.5, chunk, rot(1e4, 8), v_mix=True), None)])
+    cfg = config(97, 32, 3e-6, 2.0, 0.65, 2, [with_mlp(att(4, 2, 8, 12, 2, 0.5, chunk, rot(1e4, 8), v_mix=True), None)])
     eng, w = engine_of(cfg, 11)
     n_chunks = 3
     i = n_chunks * chunk - 1                   # the last position of the third chunk
@@ -399,9 +398,9 @@ def test_the_first_token_reaches_a_position_hundreds_of_tokens_on(kind):
     changing the sequence's first token changes the logits 330 tokens on, through a prompt and
     through tokens decoded one by one."""
     if kind == "latent":
-        cfg = config(97, 32, 1e-5, 2.0, 0.7, 3, [with_mlp(lat(3, 8, 8, 8, 16, 12, 0.6, rot(1e4, 8, (4.0, 64, 32.0, 1.0))), 24)])
+        cfg = config(97, 32, 3e-6, 2.0, 0.55, 3, [with_mlp(lat(3, 8, 8, 8, 16, 12, 0.6, rot(1e4, 8, (4.0, 64, 32.0, 1.0))), 24)])
     else:
-        cfg = config(97, 32, 1e-5, 2.0, 0.7, 3, [with_mlp(gru(48), 24)])
+        cfg = config(97, 32, 3e-6, 2.0, 0.55, 3, [with_mlp(gru(48), 24)])
     w32 = make_weights(cfg, 5, F32)
     if kind == "gru":
         w32["l0.mix.z"] = w32["l0.mix.z"] * 0.05             # gates near 0.001 whatever the token
