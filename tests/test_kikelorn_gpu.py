@@ -124,6 +124,34 @@ def test_convolution_with_its_options_in_portions_and_single_tokens(din, dout, t
             at[s] += n
 
 
+@pytest.mark.parametrize("din", [F32, BF16])
+@pytest.mark.parametrize("taps", [2, 3, 4, 6])
+def test_convolution_over_many_channels_and_sequences_that_end_inside_a_thread(din, taps):
+    """512 channels, five sequences of 1 to 301 tokens whose borders fall anywhere within the four
+    tokens a thread owns, a second step that goes on from the kept inputs, then single tokens."""
+    o = ops()
+    C = 512
+    g = torch.Generator().manual_seed(taps)
+    lens = [301, 1, 6, 2, 131]
+    extra = 9
+    u = [torch.randn(n + extra, C, generator=g).to(din) for n in lens]
+    w = (0.5 * torch.randn(C, taps, generator=g)).to(BF16)
+    refs = [q64(x, din) + P.causal_conv(q64(x, din), q64(w, BF16)) for x in u]
+    state = torch.zeros(5, taps - 1, C, dtype=torch.float32, device=DEV)
+    at = [0] * 5
+    for step in ([(i, n) for i, n in enumerate(lens)], [(0, 3), (2, 1), (4, 5)], [(i, 1) for i in range(5)], [(i, 1) for i in (4, 1, 0)]):
+        rows = torch.cat([u[i][at[i]:at[i] + n] for i, n in step]).to(DEV)
+        slot_of, cu, slots = packed(step)
+        y, cp = torch.empty(rows.shape[0], C, dtype=BF16, device=DEV), torch.empty(rows.shape[0], C, dtype=BF16, device=DEV)
+        o.causal_conv(rows, 0, C, w.to(DEV), None, state, y, slot_of, cu, slots, len(step), single_tokens=all(n == 1 for _, n in step),
+                      act=o.CONV_ACT_NONE, add_input=True, copy=cp)
+        want = torch.cat([refs[i][at[i]:at[i] + n] for i, n in step])
+        assert rel_err(y, want) < 1e-2, (taps, step)
+        assert torch.equal(cp.cpu(), rows.to(BF16).cpu())
+        for i, n in step:
+            at[i] += n
+
+
 def test_convolution_keeps_silu_and_bias_for_the_state_space_part():
     o = ops()
     C, taps = 20, 4
@@ -218,6 +246,38 @@ def test_gated_normed_scaled_add(gdt, width):
     xd = x.to(DEV)
     o.norm_add(xd, y.to(DEV), w.to(DEV), 1e-5)
     assert rel_err(xd, x.to(F) + P.norm(y.to(F), q64(w, gdt), 1e-5)) < 1e-5
+
+
+@pytest.mark.parametrize("rows", [5, 700])
+@pytest.mark.parametrize("width", [1024, 2048, 4096, 8192])
+def test_gated_normed_scaled_add_of_wide_rows_few_and_many(rows, width):
+    """The widths at which a thread keeps 1, 2, 4 and 8 groups of four values, in the form for few rows
+    (everything asked for at once) and the form for many."""
+    o = ops()
+    g = torch.Generator().manual_seed(width + rows)
+    x, y = torch.randn(rows, width, generator=g), 3.0 * torch.randn(rows, width, generator=g)
+    logits, bias, w = (2.0 * torch.randn(rows, width, generator=g)).to(BF16), torch.randn(width, generator=g).to(BF16), (1.0 + 0.3 * torch.randn(width, generator=g)).to(BF16)
+    xd = x.to(DEV)
+    o.norm_add(xd, y.to(DEV), w.to(DEV), 1e-6, mult=0.4, gate=logits.to(DEV), gate_bias=bias.to(DEV))
+    yy = y.to(F) * torch.sigmoid(q64(logits, BF16) + q64(bias, BF16))
+    assert rel_err(xd, x.to(F) + 0.4 * P.norm(yy, q64(w, BF16), 1e-6)) < 1e-5
+
+
+def test_bias_with_gelu_and_gates_in_whole_groups_of_eight():
+    o = ops()
+    g = torch.Generator().manual_seed(8)
+    for rows, cols, fill_cols in ((3, 512, 128), (300, 3072, 1024), (64, 64, 256)):
+        u, b, b2 = (2.0 * torch.randn(rows, cols, generator=g)).to(BF16), torch.randn(cols, generator=g).to(BF16), torch.randn(fill_cols, generator=g).to(BF16)
+        ud = u.to(DEV)
+        fill = torch.full((rows, fill_cols + 8), 9.0, dtype=torch.float32, device=DEV)
+        o.bias_act(ud, b.to(DEV), ud, fill=fill[:, :fill_cols], fill_bias=b2.to(DEV))        # in place, as the feed-forward runs it
+        assert rel_err(ud, P.gelu_tanh(q64(u, BF16) + q64(b, BF16))) < 1e-2
+        assert torch.equal(fill[:, :fill_cols].cpu(), b2.float().expand(rows, fill_cols)) and torch.all(fill[:, fill_cols:] == 9.0)
+        for group in (1, 64):
+            x, gl = torch.randn(rows, cols, generator=g).to(BF16), torch.randn(rows, cols // group, generator=g).to(BF16)
+            xd = x.to(DEV)
+            o.sigmoid_gate(xd, gl.to(DEV), group)
+            assert rel_err(xd, q64(x, BF16) * torch.sigmoid(q64(gl, BF16)).repeat_interleave(group, dim=1)) < 1e-2
 
 
 @pytest.mark.parametrize("dt", [F32, BF16])
@@ -320,6 +380,51 @@ def test_unequal_batches_reused_slots_and_poisoned_pages(name, dtype):
         eng.cache.check()
         eng.cache.poison()
         seqs, refs, lengths = seqs[::-1], refs[::-1], lengths[::-1]     # other sequences in the slots the first round used
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_model_of_middling_sizes_whole_in_portions_and_decoded(dtype):
+    """Width 512, heads of 64 and 128, a latent of 128 + 32, a minGRU of 768: the sizes at which the
+    bfloat16 run takes the tensor-core products and every kernel its 16-byte form."""
+    cfg = config(1000, 512, 1e-6, 22.6, 0.8, 3, [
+        with_mlp(att(8, 2, 64, 64, 4, 0.125, 150, rot(1e4, 64), v_mix=True), 1536),
+        with_mlp(lat(8, 64, 32, 64, 128, 192, 0.1, rot(1e5, 32, (8.0, 128, 16.0, 1.0))), 1024),
+        with_mlp(gru(768), 1536),
+        with_mlp(att(4, 2, 128, 64, 2, 0.09, 64, rot(5e5, 32), v_mix=True), None),
+        with_mlp(lat(4, 32, 64, 128, 256, 96, 0.1, rot(1e4, 64)), 2048)])
+    eng, w = engine_of(cfg, 7, dtype, max_tokens=4096)
+    seqs = prompts(1000, [390, 17], 3)
+    refs = [P.forward(cfg, w, s) for s in seqs]
+    slots = [eng.acquire() for _ in seqs]
+    outs = [[], []]
+    got = eng.step([S(slots[0], seqs[0][:300]), S(slots[1], seqs[1][:9])])
+    outs[0].append(got[:300].clone()), outs[1].append(got[300:].clone())
+    got = eng.step([S(slots[0], seqs[0][300:380]), S(slots[1], seqs[1][9:13])])
+    outs[0].append(got[:80].clone()), outs[1].append(got[80:].clone())
+    for k in range(4):
+        got = eng.step([S(slots[0], [seqs[0][380 + k]]), S(slots[1], [seqs[1][13 + k]])])
+        outs[0].append(got[:1].clone()), outs[1].append(got[1:].clone())
+    for k in range(4, 10):
+        outs[0].append(eng.step([S(slots[0], [seqs[0][380 + k]])]).clone())
+    assert close(torch.cat(outs[0]), refs[0], dtype) and close(torch.cat(outs[1]), refs[1], dtype)
+    for sl in slots:
+        eng.release(sl)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_step_cut_into_micro_batches_of_64_tokens(dtype):
+    """The engine cuts a step of many tokens into micro-batches; with 64 tokens each the cuts fall
+    inside the sequences, between them and at a chunk's edge, and every state has to carry over."""
+    eng, cfg, w = engine("odd", dtype, prefill_chunk_tokens=64)
+    seqs = prompts(cfg["vocab"], [200, 70, 3, 64], 13)
+    refs = [P.forward(cfg, w, s) for s in seqs]
+    slots = [eng.acquire() for _ in seqs]
+    got = eng.step([S(sl, s) for sl, s in zip(slots, seqs)])
+    assert close(got, torch.cat(refs), dtype)
+    for sl in slots:
+        eng.release(sl)
+    eng.cache.check()
 
 
 def test_batch_against_each_alone_in_float32():
