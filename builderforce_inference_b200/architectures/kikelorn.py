@@ -47,6 +47,8 @@ def kikelorn_spec(cfg: KikelornConfig) -> ModelSpec:
                 v_mix = "mix" if mixing_seen else "source"
                 mixing_seen = True
                 names["mixer.v_mix"] = q + "vmix"
+            else:       # a checkpoint may still carry the factor of a layer that does not mix
+                unused.append(q + "vmix")
             mixer = PartSpec("attention", {
                 "width": cfg.width, "n_heads": m.heads, "n_kv_heads": m.kv_heads, "head_dim": m.dim, "v_dim": m.vdim,
                 "position": _rotary(m.rot, "half"), "qk_norm": "row", "eps": cfg.eps, "scale": m.scale, "chunk": m.chunk,
