@@ -3,6 +3,8 @@
 //
 //   bfi_norm_add:      x[t, :] += mult * y'[t, :] * rsqrt(mean(y'[t, :]^2) + eps) * w   (y float32)
 //                      with y' = y, or, given gate logits g (and a bias b), y' = y * sigmoid(g + b)
+//                      and, in single-token steps when asked, the convolution over time in front of the next sublayer
+//                      on the row just made (see ConvTail);
 //                      and, when asked, the next sublayer's norm of the new x in the same kernel:
 //                      h[t, :] = x[t, :] * rsqrt(mean(x[t, :]^2) + eps2) * w2       (h in the activation dtype)
 //   bfi_weighted_sum:  out[t, :] = a * y0[t, :] + b * y1[t, :]                      (all float32)
@@ -80,6 +82,63 @@ __device__ __forceinline__ float4 load4_as_f32(const void* p, int dtype, size_t 
     return make_float4(a.x, a.y, b.x, b.y);
 }
 
+// What may follow the add in a step in which every sequence brings one token: the convolution over time that stands in
+// front of the NEXT sublayer (2 to 4 taps, no bias), on the row just made.  With the new x as the current input and the
+// slot's kept inputs as the earlier ones,
+//     h[t, c] = x[t, c] + sum_j w[c, taps-1-j] in_j[c]          plain[t, c] = x[t, c]
+// both in the activation type, and the kept inputs move on by one.  A thread owns its channels of the row in both
+// parts, so nothing is read by another thread between them.
+struct ConvTail {
+    const void* w;            // null: no tail
+    int w_dtype, taps;
+    float* state;             // [slots][taps-1][width]
+    const int* token_slot;
+    void* h;
+    long h_stride;
+    void* plain;
+    long plain_stride;
+    int out_dtype;
+};
+
+__device__ __forceinline__ void store4_from_f32(void* p, int dtype, size_t i, const float4 v) {
+    if (dtype == BFI_F32) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(p) + i) = v;
+    } else {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 packed;
+        packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+        packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(p) + i) = packed;
+    }
+}
+
+__device__ __forceinline__ void conv_tail_chunk(const ConvTail& ct, int t, int slot, int width, int c, const float4 cur) {
+    const int taps = ct.taps;
+    float* st = ct.state + (size_t)slot * (taps - 1) * width + c;
+    float4 kept[3];                                // the inputs 1, 2, 3 steps back (taps <= 4)
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const float in0[4] = {cur.x, cur.y, cur.z, cur.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) acc[k] = fmaf(load_as_f32(ct.w, ct.w_dtype, (size_t)(c + k) * taps + (taps - 1)), in0[k], acc[k]);
+#pragma unroll
+    for (int j = 1; j < 4; ++j) {
+        if (j < taps) {
+            kept[j - 1] = *reinterpret_cast<const float4*>(st + (size_t)(taps - 1 - j) * width);
+            const float in[4] = {kept[j - 1].x, kept[j - 1].y, kept[j - 1].z, kept[j - 1].w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                acc[k] = fmaf(load_as_f32(ct.w, ct.w_dtype, (size_t)(c + k) * taps + (taps - 1 - j)), in[k], acc[k]);
+        }
+    }
+    store4_from_f32(ct.h, ct.out_dtype, (size_t)t * ct.h_stride + c, make_float4(acc[0] + in0[0], acc[1] + in0[1], acc[2] + in0[2], acc[3] + in0[3]));
+    store4_from_f32(ct.plain, ct.out_dtype, (size_t)t * ct.plain_stride + c, cur);
+    // the window moves on by one: the input j steps back takes the place of the one j + 1 steps back
+    *reinterpret_cast<float4*>(st + (size_t)(taps - 2) * width) = cur;
+#pragma unroll
+    for (int j = 1; j < 3; ++j)
+        if (j < taps - 1) *reinterpret_cast<float4*>(st + (size_t)(taps - 2 - j) * width) = kept[j - 1];
+}
+
 // EARLY (few rows: a single-token step): the weights before the wait for the kernel before this one, and x asked for
 // together with y and the gate's logits, so the row costs one trip to memory instead of two; with many rows the
 // registers that takes cost more in resident rows than the trip does.
@@ -87,7 +146,7 @@ template <int VPT, bool EARLY>
 __global__ void __launch_bounds__(256)
 norm_add_vec_kernel(float* __restrict__ x, long x_stride, const float* __restrict__ y, long y_stride, const void* __restrict__ w,
                     int w_dtype, int width, float eps, float mult, const NormAddGate g, const void* __restrict__ w2, int w2_dtype,
-                    float eps2, void* __restrict__ h, int h_dtype, long h_stride) {
+                    float eps2, void* __restrict__ h, int h_dtype, long h_stride, const ConvTail ct) {
     pdl_trigger();
     __shared__ float scratch[33];
     const int t = blockIdx.x;
@@ -150,6 +209,16 @@ norm_add_vec_kernel(float* __restrict__ x, long x_stride, const float* __restric
         xr[j] = o;
         v[i] = o;
     }
+    if (ct.w != nullptr) {
+        const int slot = ct.token_slot[t];
+        if (slot >= 0) {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int j = i * 256 + threadIdx.x;
+                if (j < n4) conv_tail_chunk(ct, t, slot, width, j * 4, v[i]);
+            }
+        }
+    }
     if (h == nullptr) return;
     float ss2 = 0.0f;
 #pragma unroll
@@ -178,7 +247,9 @@ norm_add_vec_kernel(float* __restrict__ x, long x_stride, const float* __restric
 extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stride, const void* w, int w_dtype,
                             int n_rows, int width, float eps, const void* w2, int w2_dtype, float eps2, void* h,
                             int h_dtype, long h_stride, float mult, const void* gate, int gate_dtype, long gate_stride,
-                            const void* gate_bias, int gate_bias_dtype, cudaStream_t stream) {
+                            const void* gate_bias, int gate_bias_dtype, const void* conv_w, int conv_w_dtype, int conv_taps,
+                            float* conv_state, const int* token_slot, void* conv_h, long conv_h_stride, void* conv_plain,
+                            long conv_plain_stride, int conv_out_dtype, cudaStream_t stream) {
     BFI_REQUIRE(dtype_ok(w_dtype) && dtype_ok(w2_dtype) && dtype_ok(h_dtype) && dtype_ok(gate_dtype) && dtype_ok(gate_bias_dtype),
                 "norm_add: unknown dtype code");
     BFI_REQUIRE(n_rows >= 0 && width > 0, "norm_add: bad sizes rows=%d width=%d", n_rows, width);
@@ -187,13 +258,27 @@ extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stri
     BFI_REQUIRE(gate == nullptr || gate_stride >= width, "norm_add: the gate's row stride is shorter than the row");
     if (n_rows == 0) return 0;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    ConvTail ct;
+    ct.w = conv_w, ct.w_dtype = conv_w_dtype, ct.taps = conv_taps, ct.state = conv_state, ct.token_slot = token_slot;
+    ct.h = conv_h, ct.h_stride = conv_h_stride, ct.plain = conv_plain, ct.plain_stride = conv_plain_stride, ct.out_dtype = conv_out_dtype;
+    if (conv_w != nullptr) {
+        BFI_REQUIRE(dtype_ok(conv_w_dtype) && dtype_ok(conv_out_dtype), "norm_add: unknown dtype code of the convolution that follows");
+        BFI_REQUIRE(conv_taps >= 2 && conv_taps <= 4 && conv_state != nullptr && token_slot != nullptr && conv_h != nullptr &&
+                        conv_plain != nullptr && conv_h_stride >= width && conv_plain_stride >= width,
+                    "norm_add: the convolution that follows takes 2 to 4 taps, its state, the tokens' slots and two outputs of the width");
+    }
     NormAddGate g;
     g.logits = gate, g.dtype = gate_dtype, g.stride = gate_stride, g.bias = gate != nullptr ? gate_bias : nullptr;
     g.bias_dtype = gate_bias_dtype;
     const auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     // the plain normed add keeps the kernel (and with it the order of its sums) it has always had
     const auto al_for = [](const void* p, int dt) { return (reinterpret_cast<uintptr_t>(p) & (dt == BFI_F32 ? 15 : 7)) == 0; };
-    if ((gate != nullptr || mult != 1.0f) && al_for(w, w_dtype) && (gate_bias == nullptr || al_for(gate_bias, gate_bias_dtype)) && width % 4 == 0 &&
+    const auto al_out = [](const void* p, long stride, int dt) {
+        return (reinterpret_cast<uintptr_t>(p) & (dt == BFI_F32 ? 15 : 7)) == 0 && stride % 4 == 0;
+    };
+    const bool tail_ok = conv_w == nullptr || (al_out(conv_h, conv_h_stride, conv_out_dtype) && al_out(conv_plain, conv_plain_stride, conv_out_dtype) &&
+                                               (reinterpret_cast<uintptr_t>(conv_state) & 15) == 0);
+    if ((gate != nullptr || mult != 1.0f || conv_w != nullptr) && tail_ok && al_for(w, w_dtype) && (gate_bias == nullptr || al_for(gate_bias, gate_bias_dtype)) && width % 4 == 0 &&
         width <= 8 * 4 * 256 && x_stride % 4 == 0 && y_stride % 4 == 0 && al16(x) && al16(y) &&
         (gate == nullptr || (gate_stride % 4 == 0 && (((uintptr_t)gate) & (gate_dtype == BFI_F32 ? 15 : 7)) == 0))) {
         const int vpt = (width / 4 + 255) / 256;
@@ -202,10 +287,10 @@ extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stri
     do {                                                                                                                     \
     if (early)                                                                                                               \
         bfi_launch(norm_add_vec_kernel<V, true>, dim3(n_rows), dim3(256), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, \
-                   eps, mult, g, w2, w2_dtype, eps2, h, h_dtype, h_stride);                                                  \
+                   eps, mult, g, w2, w2_dtype, eps2, h, h_dtype, h_stride, ct);                                              \
     else                                                                                                                     \
         bfi_launch(norm_add_vec_kernel<V, false>, dim3(n_rows), dim3(256), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, \
-                   eps, mult, g, w2, w2_dtype, eps2, h, h_dtype, h_stride);                                                  \
+                   eps, mult, g, w2, w2_dtype, eps2, h, h_dtype, h_stride, ct);                                              \
     } while (0)
         if (vpt <= 1) BFI_NORM_ADD(1);
         else if (vpt == 2) BFI_NORM_ADD(2);
@@ -214,6 +299,7 @@ extern "C" int bfi_norm_add(float* x, long x_stride, const float* y, long y_stri
 #undef BFI_NORM_ADD
         return bfi_check_launch("norm_add");
     }
+    BFI_REQUIRE(conv_w == nullptr, "norm_add: the convolution that follows needs rows of a multiple of 4 values (at most 8192) on 16-byte borders");
     bfi_launch(norm_add_kernel, dim3(n_rows), dim3(threads), 0, stream, x, x_stride, y, y_stride, w, w_dtype, width, eps, w2,
                w2_dtype, eps2, h, h_dtype, h_stride, mult, g);
     return bfi_check_launch("norm_add");

@@ -159,7 +159,12 @@ class Decoder:
         """Schedule entries ``first .. last-1`` (all of them by default)."""
         last = len(self.spec.schedule) if last is None else last
         for i in range(first, last):
+            # a block may make the first input of the run after it (``ctx.extras``): it is told which that is
+            follows = i + 1 < last
+            ctx.extras["next_block"] = self.blocks[self.spec.schedule[i + 1].layer] if follows else None
+            ctx.extras["next_run"] = cache.run_cache(i + 1) if follows else None
             self.blocks[self.spec.schedule[i].layer].forward(ctx, x, cache.run_cache(i))
+        ctx.extras.pop("outnorm.input", None)
 
     def logits(self, ctx, x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
         """Final norm and head at the given rows of ``x``; ``out`` is float32 ``[len(rows), vocab]``."""

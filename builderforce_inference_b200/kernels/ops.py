@@ -457,13 +457,32 @@ def _f32_vector(t: Optional[torch.Tensor], n: int, what: str) -> None:
 
 def norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, next_w: Optional[torch.Tensor] = None,
              next_eps: float = 0.0, out: Optional[torch.Tensor] = None, mult: float = 1.0,
-             gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None) -> None:
+             gate: Optional[torch.Tensor] = None, gate_bias: Optional[torch.Tensor] = None, conv=None) -> None:
     """``x[t] += mult * y[t] * rsqrt(mean(y[t]^2) + eps) * w``: a sublayer's output, normed, into the
     float32 residual stream.  With ``gate`` (logits ``[rows, width]`` of either storage type, and an
     optional ``gate_bias`` ``[width]``) ``y`` is first multiplied by ``sigmoid(gate + gate_bias)``.
     With ``next_w`` and ``out`` the next sublayer's norm of the new ``x`` is made in the same
-    kernel: ``out[t] = x[t] * rsqrt(mean(x[t]^2) + next_eps) * next_w``."""
+    kernel: ``out[t] = x[t] * rsqrt(mean(x[t]^2) + next_eps) * next_w``.  ``conv`` (for steps in
+    which every sequence brings one token; rows of a multiple of 4 values): ``(w, state, token_slot,
+    h, plain)``, the convolution over time that stands in front of the NEXT sublayer, made from
+    the row just written: ``h[t] = x[t] + conv(x)[t]`` with ``w`` ``[width, taps]`` (2 to 4 taps) and
+    the kept inputs ``state`` ``[slots, taps-1, width]``, which move on by one; ``plain[t] = x[t]``; both
+    outputs in one storage type."""
     _need_cuda(x, y, w, next_w, out, gate, gate_bias)
+    cw = cstate = cslot = ch = cplain = None
+    if conv is not None:
+        cw, cstate, cslot, ch, cplain = conv
+        _need_cuda(cw, cstate, cslot, ch, cplain)
+        _i32(cslot, "token slots")
+        _rows_2d(ch, "convolved rows")
+        _rows_2d(cplain, "plain rows")
+        taps = cw.shape[1] if cw.dim() == 2 else 0
+        if cw.shape != (x.shape[1], taps) or not cw.is_contiguous() or not 2 <= taps <= 4:
+            raise KernelError(f"norm_add: the convolution that follows takes contiguous weights [{x.shape[1]}, 2 to 4 taps]")
+        if cstate.dtype != torch.float32 or not cstate.is_contiguous() or tuple(cstate.shape[1:]) != (taps - 1, x.shape[1]):
+            raise KernelError("norm_add: the convolution's state must be contiguous float32 [slots, taps-1, width]")
+        if ch.shape != x.shape or cplain.shape != x.shape or ch.dtype != cplain.dtype or cslot.numel() < x.shape[0]:
+            raise KernelError("norm_add: the convolution's outputs have the stream's shape and one dtype; a slot per row")
     if gate is not None:
         _rows_2d(gate, "gate logits")
         if gate.shape != x.shape:
@@ -490,7 +509,11 @@ def norm_add(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, next
                          c_int(0 if out is None else dtype_code(out.dtype)), c_long(0 if out is None else out.stride(0)),
                          c_float(mult), _ptr(gate), c_int(0 if gate is None else dtype_code(gate.dtype)),
                          c_long(0 if gate is None else gate.stride(0)), _ptr(gate_bias),
-                         c_int(0 if gate_bias is None else dtype_code(gate_bias.dtype)), _stream())
+                         c_int(0 if gate_bias is None else dtype_code(gate_bias.dtype)), _ptr(cw),
+                         c_int(0 if cw is None else dtype_code(cw.dtype)), c_int(0 if cw is None else cw.shape[1]), _ptr(cstate),
+                         _ptr(cslot), _ptr(ch), c_long(0 if ch is None else ch.stride(0)), _ptr(cplain),
+                         c_long(0 if cplain is None else cplain.stride(0)), c_int(0 if ch is None else dtype_code(ch.dtype)),
+                         _stream())
 
 
 def weighted_sum(out: torch.Tensor, y0: torch.Tensor, a: float, y1: torch.Tensor, b: float) -> None:

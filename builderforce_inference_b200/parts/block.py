@@ -18,8 +18,11 @@ the mixer's and the feed-forward's last matrix product.
               with ``gate``, ``sigmoid(W_g x + b_g)`` element by element, made from the residual stream
               as it stands before the convolution.  One kernel reads the float32 stream and writes
               both the convolved and the plain copy in the activation dtype; one kernel gates, norms,
-              scales and adds the sublayer's float32 output.  The feed-forward (with its norm,
-              convolution and gate) may be absent.
+              scales and adds the sublayer's float32 output.  In steps in which every sequence
+              brings one token that kernel also makes the input of the sublayer that follows (the next
+              convolution, of this block or of the out-norm block that runs next) from the row it has
+              just written, so a sublayer costs one launch around it instead of two.  The feed-forward
+              (with its norm, convolution and gate) may be absent.
 """
 from __future__ import annotations
 
@@ -196,30 +199,61 @@ class OutNormBlock(Block):
                         ctx.n_seqs, single_tokens=single, act=ops.CONV_ACT_NONE, add_input=True, copy=plain)
         return h, plain
 
-    def _output(self, ctx, x, y, plain, i: int, norm) -> None:
+    def _output(self, ctx, x, y, plain, i: int, norm, follow=None):
+        """The sublayer's output into the stream.  ``follow`` ``(weights, kept inputs)``: the convolution
+        in front of the sublayer that runs next, made in the same kernel; returns its two outputs."""
         glog = None
         if self.has_gate:
             glog = ctx.rows("block.gate", self.width)
             linear(plain, self.gate_w[i], glog, EPI_STORE)
-        norm.add_to(ctx, x, y, mult=self.mult, gate=glog, gate_bias=self.gate_b[i])
+        conv = made = None
+        if follow is not None:
+            made = (ctx.rows("block.in", self.width), ctx.rows("block.plain", self.width))
+            conv = (follow[0], follow[1], ctx.token_slot) + made
+        norm.add_to(ctx, x, y, mult=self.mult, gate=glog, gate_bias=self.gate_b[i], conv=conv)
+        return made
+
+    def follows_in_one_kernel(self, ctx) -> bool:
+        """Whether the convolution in front of this block's sublayers can ride on the kernel behind the
+        sublayer before: single-token steps, 2 to 4 taps, rows in whole groups of 8 values, a gate."""
+        return self.has_gate and self.taps is not None and 2 <= self.taps <= 4 and self.width % 8 == 0 \
+            and ctx.max_seq_tokens == 1 and ctx.n_tokens == ctx.n_seqs
+
+    def _kept(self, run) -> list:
+        own = self._own_needs()
+        return list(run.entries[len(run.entries) - len(own):]) if own else [self.no_history] * self.n_sub
 
     def forward(self, ctx, residual, run) -> None:
         import torch
         if not run.writes_cache:
             raise RuntimeError("an out-norm block keeps its convolutions' inputs: its run needs a cache of its own")
-        own = self._own_needs()
-        n_mixer = len(run.entries) - len(own)
+        n_mixer = len(run.entries) - len(self._own_needs())
         entries = tuple(run.entries[:n_mixer])
-        kept = list(run.entries[n_mixer:]) if own else [self.no_history] * self.n_sub
+        kept = self._kept(run)
         kv = next((e for e in entries if isinstance(e, KVView)), None)
         state = next((e for e in entries if not isinstance(e, KVView)), None)
         mixer_run = RunCache(kv=kv, state=state, writes_cache=True, entries=entries)
         y = ctx.rows("sublayer.out", self.width, torch.float32)
-        h, plain = self._input(ctx, residual, 0, kept[0])
+        fused = self.follows_in_one_kernel(ctx)
+        # what the run after this one is, when it is an out-norm block of the same width: its first input is made here
+        after = ctx.extras.get("next_block")
+        after_run = ctx.extras.get("next_run")
+        to_next = None
+        if fused and isinstance(after, OutNormBlock) and after is not self and after.width == self.width \
+                and after.follows_in_one_kernel(ctx) and after_run is not None and after_run.writes_cache:
+            to_next = (after.conv_w[0], after._kept(after_run)[0])
+        made = ctx.extras.pop("outnorm.input", None)
+        if made is not None and made[0] is self:
+            h, plain = made[1]
+        else:
+            h, plain = self._input(ctx, residual, 0, kept[0])
         self._mixer.forward_store(ctx, h, y, mixer_run)
-        self._output(ctx, residual, y, plain, 0, self.norm1)
         if self.ffn is None:
-            return
-        h, plain = self._input(ctx, residual, 1, kept[1])
-        self.ffn.forward_store(ctx, h, y)
-        self._output(ctx, residual, y, plain, 1, self.norm2)
+            made = self._output(ctx, residual, y, plain, 0, self.norm1, follow=to_next)
+        else:
+            made = self._output(ctx, residual, y, plain, 0, self.norm1, follow=(self.conv_w[1], kept[1]) if fused else None)
+            h, plain = made if made is not None else self._input(ctx, residual, 1, kept[1])
+            self.ffn.forward_store(ctx, h, y)
+            made = self._output(ctx, residual, y, plain, 1, self.norm2, follow=to_next)
+        if to_next is not None:
+            ctx.extras["outnorm.input"] = (after, made)

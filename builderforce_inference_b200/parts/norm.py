@@ -35,13 +35,13 @@ class RMSNorm(Norm):
         ops.rmsnorm(x, self.weight, self.eps, out, rows)
         return out
 
-    def add_to(self, ctx, residual, y, then=None, mult: float = 1.0, gate=None, gate_bias=None):
+    def add_to(self, ctx, residual, y, then=None, mult: float = 1.0, gate=None, gate_bias=None, conv=None):
         """``residual += mult * norm(y)``: both float32 ``[tokens, width]``.  With ``gate`` (logits of
         the stream's shape, and an optional bias) ``y`` is first multiplied by ``sigmoid(gate + bias)``.
         With ``then`` (the norm that reads the residual stream next) its output is made in the same
-        kernel and returned."""
+        kernel and returned.  ``conv``: see ``ops.norm_add``."""
         if not isinstance(then, RMSNorm):
-            ops.norm_add(residual, y, self.weight, self.eps, mult=mult, gate=gate, gate_bias=gate_bias)
+            ops.norm_add(residual, y, self.weight, self.eps, mult=mult, gate=gate, gate_bias=gate_bias, conv=conv)
             return None if then is None else then.forward(ctx, residual)
         out = ctx.rows("norm.out", then.width)
         ops.norm_add(residual, y, self.weight, self.eps, next_w=then.weight, next_eps=then.eps, out=out, mult=mult,

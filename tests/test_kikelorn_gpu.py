@@ -263,6 +263,42 @@ def test_gated_normed_scaled_add_of_wide_rows_few_and_many(rows, width):
     assert rel_err(xd, x.to(F) + 0.4 * P.norm(yy, q64(w, BF16), 1e-6)) < 1e-5
 
 
+@pytest.mark.parametrize("odt", [F32, BF16])
+@pytest.mark.parametrize("taps", [2, 3, 4])
+@pytest.mark.parametrize("width", [40, 2048])
+def test_gated_normed_add_that_also_makes_the_next_convolution(odt, taps, width):
+    """Single-token steps: the kernel behind a sublayer also makes the input of the next one from the
+    row it has just written and the slots' kept inputs, and moves those on; three steps in a row over
+    slots 5, 0 and 3 (and a padding row) against the plain convolution over the rows so far."""
+    o = ops()
+    g = torch.Generator().manual_seed(taps * width)
+    slots = [5, 0, 3]
+    cw = (0.4 * torch.randn(width, taps, generator=g)).to(odt)
+    nw, gb = (1.0 + 0.2 * torch.randn(width, generator=g)).to(odt), torch.randn(width, generator=g).to(odt)
+    state = torch.zeros(6, taps - 1, width, dtype=torch.float32, device=DEV)
+    seen = {s: [] for s in slots}                      # the rows of x each slot has brought so far
+    slot_of = i32(slots + [-1])
+    for step in range(3):
+        x, y = torch.randn(4, width, generator=g), 2.0 * torch.randn(4, width, generator=g)
+        gl = torch.randn(4, width, generator=g).to(odt)
+        xd = x.to(DEV)
+        h = torch.full((4, width), 7.0, dtype=odt, device=DEV)
+        plain = torch.full((4, width), 7.0, dtype=odt, device=DEV)
+        o.norm_add(xd, y.to(DEV), nw.to(DEV), 1e-5, mult=0.6, gate=gl.to(DEV), gate_bias=gb.to(DEV),
+                   conv=(cw.to(DEV), state, slot_of, h, plain))
+        want_x = x.to(F) + 0.6 * P.norm(y.to(F) * torch.sigmoid(q64(gl, odt) + q64(gb, odt)), q64(nw, odt), 1e-5)
+        assert rel_err(xd, want_x) < 1e-5
+        for r, s_ in enumerate(slots):
+            seen[s_].append(xd[r].to(F).cpu())
+            rows = torch.stack(seen[s_])
+            want_h = (rows + P.causal_conv(rows, q64(cw, odt)))[-1]
+            assert rel_err(h[r], want_h) < (1e-5 if odt == F32 else 1e-2), (step, r)
+            assert torch.equal(plain[r].cpu(), xd[r].to(odt).cpu())
+            kept = rows[-(taps - 1):]
+            assert torch.allclose(state[s_][taps - 1 - kept.shape[0]:].cpu().to(F), kept)
+        assert torch.all(h[3] == 7.0) and torch.all(state[[1, 2, 4]] == 0.0)      # the padding row and other slots are left alone
+
+
 def test_bias_with_gelu_and_gates_in_whole_groups_of_eight():
     o = ops()
     g = torch.Generator().manual_seed(8)
